@@ -1,0 +1,66 @@
+"""Builds ``libanemoi_sm100.so`` in-tree with nvcc for sm_100a (no other target)."""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+PACKAGE = Path(__file__).resolve().parent
+CSRC = PACKAGE / "csrc"
+LIBRARY = PACKAGE / "libanemoi_sm100.so"
+SOURCES = ("prepare.cu", "draft.cu", "route.cu", "attention.cu", "assemble.cu")
+FLAGS = (
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+)
+
+
+def _nvcc() -> str:
+    found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(found):
+        raise RuntimeError("nvcc not found; the sm_100a library cannot be built")
+    return found
+
+
+def needs_build() -> bool:
+    if not LIBRARY.exists():
+        return True
+    stamp = LIBRARY.stat().st_mtime
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PACKAGE.parent / "include" / "anemoi_sm100.h"]
+    return any(d.stat().st_mtime > stamp for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every CUDA source and link the shared library next to the package."""
+    if not force and not needs_build():
+        return LIBRARY
+    nvcc = _nvcc()
+    objects = []
+    procs = []
+    out_dir = PACKAGE / "build"
+    out_dir.mkdir(exist_ok=True)
+    for name in SOURCES:
+        obj = out_dir / (name + ".o")
+        cmd = [nvcc, *FLAGS, "-c", str(CSRC / name), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((name, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objects.append(str(obj))
+    for name, proc in procs:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {name}:\n{out}")
+        if verbose and out:
+            print(out)
+    link = [nvcc, "-shared", "-o", str(LIBRARY), *objects, "-gencode", "arch=compute_100a,code=sm_100a",
+            "-Xcompiler", "-fPIC", "-lcudart"]
+    done = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if done.returncode != 0:
+        raise RuntimeError(f"link failed:\n{done.stdout}")
+    return LIBRARY
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose=True))

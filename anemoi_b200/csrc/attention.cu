@@ -1,0 +1,671 @@
+// Block-sparse mixed-precision flash attention for sm_100a.
+//
+// One CTA owns one query tile (QB rows of one head, padded to the 128-row MMA
+// shape) and walks that tile's ragged list of 64-key stages in the order
+// NVFP4 -> INT8 -> FP16 with one online-softmax state.
+//
+// Warp roles (192 threads):
+//   warps 0-3  softmax: thread r owns query row r == TMEM lane r
+//   warp 4     loader: one lane issues 1-D bulk copies (TMA engine) of the Q
+//              record of each phase and of one K|V record per stage into a ring
+//              of shared-memory slots, completion counted on mbarriers
+//   warp 5     MMA: allocates TMEM; one lane issues tcgen05.mma
+//                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
+//                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
+//              and tcgen05.commit to mbarriers
+// TMEM columns: S [0,64), O [64,64+D), NVFP4 scale factors [192,216).
+// O stays in TMEM across all stages; it is rescaled (read-modify-write by the
+// softmax threads) only when some row's running maximum moved, and at a phase
+// change, where it is also converted between the phases' value domains.
+//
+// Numerics follow the reference's phases
+// (csrc/attention/cuda/sm120/q64_attention_phase_composer.inl:1-146, 506-932,
+// 934-1331; primitives/qattn/attn_utils.cuh:363-389, 470-625):
+//   base-2 online softmax, sigma = log2(e)/sqrt(D), m0 = -5e6, keys >= valid_k masked,
+//   denominator accumulated from the unquantised P,
+//   NVFP4: score scale sigma*q_gs*k_gs, P -> e2m1(6P) with a constant 448 block scale,
+//          O_true = O * v_gs/(6*448)
+//   INT8 : exact s32 scores, scale sigma*q_scale*k_scale[stage], P -> e4m3(P*2^8.807),
+//          O_true[c] = O[c] * v_scale[c] * 2^-8.807
+//   FP16 : P -> f16
+// Accumulation is fp32 in TMEM (the reference accumulates a stage in fp16 for the
+// INT8 and FP16 cells).
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "records.cuh"
+#include "sm100_primitives.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr int kColS = 0;
+constexpr int kColO = 64;
+constexpr int kColSfaQ = 192;  // 2 k-steps x 4 columns
+constexpr int kColSfbK = 200;  // 2 k-steps x 4 columns
+constexpr int kColSfaP = 208;
+constexpr int kColSfbV = 212;
+constexpr int kMaxSlots = 4;
+constexpr float kFp8Offset = 8.807f;
+
+enum Cell : int { kNv = 0, kI8 = 1, kF16 = 2 };
+
+struct AttnParams {
+  anemoi_sm100_shape s;
+  anemoi_sm100_operands o;
+  const int32_t* row_offset;
+  const int32_t* row_counts;
+  const int32_t* stage_ids;
+  int64_t capacity;
+  const int32_t* valid_k;
+  __half* out;       // [H][tiles*QB][D]
+  int32_t* status;
+  int dense_prefix;  // 1: prefix query tiles, INT8 cell over every stage
+  int stages;        // 64-key stages per head
+  int q_tiles_int8;  // records per head in q_int8 (R + prefix query tiles)
+  int out_rows;      // rows per head in `out`
+  int nslot;
+  int slot_bytes;
+  int q_region;      // bytes
+  int p_region;      // bytes
+};
+
+struct Barriers {
+  uint64_t kv_full[kMaxSlots];
+  uint64_t kv_free[kMaxSlots];
+  uint64_t q_full, q_free, s_full, s_free, p_full, o_done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait shared by all roles: gives up after ~2 s or when another thread
+// of the CTA gave up, recording `where` in the status word.
+__device__ __forceinline__ bool wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
+                                     int where) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (b->abort) return false;
+    if ((spin & 1023u) == 1023u) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > 2000000000ull) break;
+    }
+  }
+  b->abort = 1;
+  atomicCAS(status, 0, where);
+  return false;
+}
+
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v),
+               "r"(v), "r"(v), "r"(v)
+               : "memory");
+}
+
+template <int D>
+struct CellInfo {
+  // bytes per stage record and per Q record, chunk counts (16-byte chunks per row)
+  __device__ static int kv_bytes(int cell) {
+    return cell == kNv ? (int)rec::kv_nvfp4_bytes(D)
+                       : (cell == kI8 ? (int)rec::kv_int8_bytes(D) : (int)rec::kv_fp16_bytes(D));
+  }
+  __device__ static int q_bytes(int cell, int qb) {
+    return cell == kNv ? (int)rec::q_nvfp4_bytes(qb, D)
+                       : (cell == kI8 ? (int)rec::q_int8_bytes(qb, D) : (int)rec::q_fp16_bytes(qb, D));
+  }
+};
+
+// ------------------------------------------------------------------------------------------
+// softmax side
+// ------------------------------------------------------------------------------------------
+struct RowState {
+  float m, d;
+};
+
+// O[row][c] *= alpha * colf[c] (colf may be null) for the thread's row.
+template <int D>
+__device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const float* colf) {
+#pragma unroll 1
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld32(tmem_row + kColO + c0, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float v = __uint_as_float(r[j]) * alpha;
+      if (colf != nullptr) v *= colf[c0 + j];
+      r[j] = __float_as_uint(v);
+    }
+    tmem_st32(tmem_row + kColO + c0, r);
+  }
+  tmem_wait_st();
+}
+
+template <int CELL>
+__device__ __forceinline__ void write_p(uint8_t* p_smem, int row, const float (&p)[64]) {
+  if (CELL == kF16) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint4 v;
+      __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j * 8 + 2 * i], p[j * 8 + 2 * i + 1]);
+      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 8)) = v;
+    }
+  } else if (CELL == kI8) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 v;
+      uint16_t* h = reinterpret_cast<uint16_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        h[i] = __nv_cvt_float2_to_fp8x2(make_float2(p[j * 16 + 2 * i], p[j * 16 + 2 * i + 1]),
+                                        __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 4)) = v;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint4 v;
+      uint8_t* h = reinterpret_cast<uint8_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        h[i] = __nv_cvt_float2_to_fp4x2(
+            make_float2(p[j * 32 + 2 * i] * 6.0f, p[j * 32 + 2 * i + 1] * 6.0f), __NV_E2M1,
+            cudaRoundNearest);
+      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 2)) = v;
+    }
+  }
+}
+
+// One stage of one phase for the thread's row.  Returns false on an aborted wait.
+template <int CELL, int D>
+__device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
+                                              const float* colf, uint32_t tmem_row, int row, int g,
+                                              bool phase_first, float score_scale, int valid,
+                                              bool live_warp, RowState& st) {
+  if (!wait(b, &b->s_full, g & 1, p.status, 10 + CELL)) return false;
+  tc_fence_after_sync();
+  if (!live_warp) {
+    // padding rows of a 64-row tile: keep the barrier protocol, skip the math
+    mbar_arrive(&b->s_free);
+    if (g > 0 && !wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
+    mbar_arrive(&b->p_full);
+    return true;
+  }
+  float s[64];
+  {
+    uint32_t r[32];
+    tmem_ld32(tmem_row + kColS, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      s[j] = CELL == kI8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+    tmem_ld32(tmem_row + kColS + 32, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      s[32 + j] = CELL == kI8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+  }
+  tc_fence_before_sync();
+  mbar_arrive(&b->s_free);
+
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) mx = fmaxf(mx, j < valid ? s[j] : -INFINITY);
+  const float m_new = fmaxf(st.m, mx * score_scale);
+  const float alpha = ex2(st.m - m_new);
+  const float bias = CELL == kI8 ? kFp8Offset - m_new : -m_new;
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    const float e = j < valid ? ex2(fmaf(s[j], score_scale, bias)) : 0.0f;
+    s[j] = e;
+    sum += e;
+  }
+  if (CELL == kI8) sum *= 0.0022326917f;  // 2^-8.807
+  st.d = st.d * alpha + sum;
+  st.m = m_new;
+
+  if (g > 0) {
+    // PV of the previous stage must be complete before P is overwritten or O rescaled.
+    if (!wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
+    tc_fence_after_sync();
+    const bool need = phase_first || __any_sync(0xffffffffu, alpha != 1.0f);
+    if (need) rescale_o<D>(tmem_row, alpha, phase_first ? colf : nullptr);
+  }
+  write_p<CELL>(p_smem, row, s);
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  mbar_arrive(&b->p_full);
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------
+// MMA side
+// ------------------------------------------------------------------------------------------
+template <int D>
+__device__ __forceinline__ void issue_qk(int cell, uint32_t tmem, uint32_t q_addr, uint32_t k_addr,
+                                         uint32_t kv_slot_addr) {
+  if (cell == kF16) {
+    constexpr uint32_t chunks = D / 8;
+    const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, 64, 0, 0);
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k)
+      mma_f16_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+  } else if (cell == kI8) {
+    constexpr uint32_t chunks = D / 16;
+    const uint32_t idesc = instr_desc(kFmtS8, kFmtS8, kAccS32, 128, 64, 0, 0);
+#pragma unroll
+    for (int k = 0; k < D / 32; ++k)
+      mma_i8_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+                smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+  } else {
+    constexpr uint32_t chunks = D / 32;
+    const uint32_t idesc = instr_desc_nvf4(128, 64);
+    const uint32_t ksf = kv_slot_addr + rec::kv_nvfp4_ksf_offset(D);
+#pragma unroll
+    for (int k = 0; k < D / 64; ++k)
+      tmem_cp_32x128b_warpx4(tmem + kColSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128));
+#pragma unroll
+    for (int k = 0; k < D / 64; ++k)
+      mma_nvf4_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+                  smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0,
+                  tmem + kColSfaQ + 4 * k, tmem + kColSfbK + 4 * k);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void issue_pv(int cell, uint32_t tmem, uint32_t p_addr,
+                                         uint32_t kv_slot_addr, uint32_t accumulate) {
+  if (cell == kF16) {
+    const uint32_t v_addr = kv_slot_addr + 64 * D * 2;
+    const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, D, 0, 1);
+    constexpr uint32_t v_lbo = (D / 8) * 128;  // between 8-key groups
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      mma_f16_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 8 * 128),
+                 smem_desc(v_addr + k * 2 * v_lbo, v_lbo, 128), idesc, accumulate | (k > 0));
+  } else if (cell == kI8) {
+    const uint32_t v_addr = kv_slot_addr + 64 * D;
+    const uint32_t idesc = instr_desc(kFmtE4M3, kFmtE4M3, kAccF32, 128, D, 0, 0);
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      mma_f8_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 4 * 128),
+                smem_desc(v_addr + k * 256, 128, 4 * 128), idesc, accumulate | (k > 0));
+  } else {
+    const uint32_t v_addr = kv_slot_addr + rec::kv_nvfp4_v_offset(D);
+    const uint32_t vsf = kv_slot_addr + rec::kv_nvfp4_vsf_offset(D);
+    const uint32_t idesc = instr_desc_nvf4(128, D);
+    tmem_cp_32x128b_warpx4(tmem + kColSfbV, smem_desc(vsf, 128, 128));
+    mma_nvf4_ss(tmem + kColO, smem_desc(p_addr, 128, 2 * 128), smem_desc(v_addr, 128, 2 * 128),
+                idesc, accumulate, tmem + kColSfaP, tmem + kColSfbV);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int QB = p.s.query_block;
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- this tile's work list ----
+  int cnt[3];
+  const int32_t* list;
+  if (p.dense_prefix) {
+    cnt[0] = 0;
+    cnt[1] = p.stages;
+    cnt[2] = 0;
+    list = nullptr;
+  } else {
+    const int32_t* rc = p.row_counts + ((int64_t)head * p.s.video_blocks + tile) * 4;
+    cnt[0] = rc[0];
+    cnt[1] = rc[1];
+    cnt[2] = rc[2];
+    list = p.stage_ids + (int64_t)head * p.capacity +
+           p.row_offset[(int64_t)head * p.s.video_blocks + tile];
+  }
+  const int total = cnt[0] + cnt[1] + cnt[2];
+  if (total == 0) return;
+
+  uint8_t* q_smem = smem;
+  uint8_t* p_smem = smem + p.q_region;
+  uint8_t* slots = p_smem + p.p_region;
+  float* colf = reinterpret_cast<float*>(slots + (size_t)p.nslot * p.slot_bytes);
+  Barriers* b = reinterpret_cast<Barriers*>(colf + D);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kMaxSlots; ++i) {
+      mbar_init(&b->kv_full[i], 1);
+      mbar_init(&b->kv_free[i], 1);
+    }
+    mbar_init(&b->q_full, 1);
+    mbar_init(&b->q_free, 1);
+    mbar_init(&b->s_full, 1);
+    mbar_init(&b->s_free, 128);
+    mbar_init(&b->p_full, 128);
+    mbar_init(&b->o_done, 1);
+    b->abort = 0;
+    mbar_init_fence();
+  }
+  // Query rows beyond QB (64-row tiles padded to the 128-row MMA shape) are never
+  // initialised: rows are independent, their results stay in TMEM lanes nobody reads.
+  if (warp == 5) {
+    tmem_alloc(&b->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = b->tmem_base;
+
+  const int q_index_fp = head * p.s.video_blocks + tile;  // q_fp16 / q_nvfp4 record
+  const int64_t q_index_i8 =
+      (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : tile);
+  const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
+
+  if (warp == 4) {
+    // =============================== loader ===============================
+    if (lane == 0) {
+      int g = 0, phase_ord = 0;
+      bool ok = true;
+      for (int cell = 0; cell < 3 && ok; ++cell) {
+        if (cnt[cell] == 0) continue;
+        if (phase_ord > 0) ok = wait(b, &b->q_free, (phase_ord - 1) & 1, p.status, 1);
+        if (!ok) break;
+        const int qbytes = CellInfo<D>::q_bytes(cell, QB);
+        const uint8_t* qsrc =
+            cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
+            : cell == kI8 ? static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes
+                          : static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes;
+        mbar_arrive_expect_tx(&b->q_full, qbytes);
+        if (cell == kNv && QB == 64) {
+          // codes fill the first half of the 128-row tile; scale blocks follow the full tile
+          const int codes = QB * D / 2;
+          bulk_g2s(q_smem, qsrc, codes, &b->q_full);
+          bulk_g2s(q_smem + 128 * D / 2, qsrc + codes, qbytes - codes, &b->q_full);
+        } else {
+          bulk_g2s(q_smem, qsrc, qbytes, &b->q_full);
+        }
+        const int kvbytes = CellInfo<D>::kv_bytes(cell);
+        const uint8_t* kvbase =
+            (cell == kNv ? static_cast<const uint8_t*>(p.o.kv_nvfp4)
+             : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
+                           : static_cast<const uint8_t*>(p.o.kv_fp16)) +
+            (int64_t)head * p.stages * kvbytes;
+        const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+        for (int i = 0; i < cnt[cell] && ok; ++i, ++g) {
+          const int slot = g % p.nslot, use = g / p.nslot;
+          if (use > 0) ok = wait(b, &b->kv_free[slot], (use - 1) & 1, p.status, 2);
+          if (!ok) break;
+          const int stage = list ? list[first + i] : i;
+          mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes);
+          bulk_g2s(slots + (size_t)slot * p.slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
+                   &b->kv_full[slot]);
+        }
+        ++phase_ord;
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issue ===============================
+    if (lane == 0) {
+      int g = 0, phase_ord = 0;
+      bool ok = true;
+      const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+      for (int cell = 0; cell < 3 && ok; ++cell) {
+        if (cnt[cell] == 0) continue;
+        ok = wait(b, &b->q_full, phase_ord & 1, p.status, 3);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (cell == kNv) {
+          const uint32_t qsf = q_addr + 128 * D / 2;
+#pragma unroll
+          for (int k = 0; k < D / 64; ++k)
+            tmem_cp_32x128b_warpx4(tmem + kColSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128));
+        }
+        const int n = cnt[cell];
+        // software pipeline: QK of stage i+1 is issued before PV of stage i
+        for (int i = 0; i <= n && ok; ++i) {
+          if (i < n) {
+            const int gi = g + i;
+            const int slot = gi % p.nslot, use = gi / p.nslot;
+            ok = wait(b, &b->kv_full[slot], use & 1, p.status, 4);
+            if (ok && gi > 0) ok = wait(b, &b->s_free, (gi - 1) & 1, p.status, 5);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * p.slot_bytes);
+            issue_qk<D>(cell, tmem, q_addr, slot_addr, slot_addr);
+            mma_commit(&b->s_full);
+            if (i == n - 1) mma_commit(&b->q_free);
+          }
+          if (i > 0) {
+            const int gj = g + i - 1;
+            const int slot = gj % p.nslot;
+            ok = wait(b, &b->p_full, gj & 1, p.status, 6);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * p.slot_bytes);
+            issue_pv<D>(cell, tmem, p_addr, slot_addr, gj > 0);
+            mma_commit(&b->o_done);
+            mma_commit(&b->kv_free[slot]);
+          }
+        }
+        g += n;
+        ++phase_ord;
+      }
+    }
+  } else {
+    // =============================== softmax rows ===============================
+    const int row = threadIdx.x;
+    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
+    RowState st{-5.0e6f, 0.0f};
+    bool ok = true;
+    int g = 0;
+    int prev_cell = -1;
+    const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
+    const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
+    const bool live_warp = warp * 32 < QB;
+    if (cnt[kNv] > 0) {
+      tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
+      tmem_wait_st();
+    }
+    for (int cell = 0; cell < 3 && ok; ++cell) {
+      if (cnt[cell] == 0) continue;
+      if (prev_cell >= 0) {
+        // per-channel factor that moves O from the previous phase's domain into this one's
+        __syncwarp();
+        asm volatile("bar.sync 1, 128;");
+        for (int c = threadIdx.x; c < D; c += 128) {
+          const float from = prev_cell == kNv ? nv_dom
+                                              : (prev_cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f);
+          const float to = cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f;
+          colf[c] = to == 0.0f ? 0.0f : from / to;
+        }
+        asm volatile("bar.sync 1, 128;");
+      }
+      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      const float q_scale =
+          cell == kI8 ? p.o.q_int8_scale[q_index_i8] : 1.0f;
+      const float base_scale =
+          cell == kNv ? sigma * p.s.q_global_scale * p.s.k_global_scale : sigma;
+      for (int i = 0; i < cnt[cell] && ok; ++i, ++g) {
+        const int stage = list ? list[first + i] : i;
+        const int valid = p.valid_k[stage];
+        const bool phase_first = i == 0 && prev_cell >= 0;
+        if (cell == kNv) {
+          ok = softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, base_scale,
+                                     valid, live_warp, st);
+        } else if (cell == kI8) {
+          const float sc = sigma * (q_scale * p.o.k_int8_scale[(int64_t)head * p.stages + stage]);
+          ok = softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, sc, valid,
+                                     live_warp, st);
+        } else {
+          ok = softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first,
+                                      base_scale, valid, live_warp, st);
+        }
+      }
+      prev_cell = cell;
+    }
+    // ---- epilogue: O_true / d -> fp16, packed row order ----
+    if (ok) ok = wait(b, &b->o_done, (g - 1) & 1, p.status, 7);
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / st.d;
+      const bool live = row < QB;
+      __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)tile * QB + row) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_row + kColO + c0, r);
+        tmem_wait_ld();
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float a = __uint_as_float(r[j + 2 * i]), c = __uint_as_float(r[j + 2 * i + 1]);
+              if (prev_cell == kNv) {
+                a *= nv_dom;
+                c *= nv_dom;
+              } else if (prev_cell == kI8) {
+                a *= vscale[c0 + j + 2 * i] * 0.0022326917f;
+                c *= vscale[c0 + j + 2 * i + 1] * 0.0022326917f;
+              }
+              h[i] = __floats2half2_rn(a * inv, c * inv);
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + j) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int D>
+int launch(AttnParams& p, int tiles, cudaStream_t st) {
+  const int QB = p.s.query_block;
+  int q_region = 0, p_region = 0, slot = 0;
+  const bool nv = p.s.has_nvfp4 && !p.dense_prefix, f16 = p.s.has_fp16 && !p.dense_prefix;
+  if (nv) {
+    q_region = max(q_region, 128 * D / 2 + (D / 64) * 512);
+    p_region = max(p_region, 128 * 32);
+    slot = max(slot, (int)rec::kv_nvfp4_bytes(D));
+  }
+  if (p.s.has_int8) {
+    q_region = max(q_region, 128 * D);
+    p_region = max(p_region, 128 * 64);
+    slot = max(slot, (int)rec::kv_int8_bytes(D));
+  }
+  if (f16) {
+    q_region = max(q_region, 128 * D * 2);
+    p_region = max(p_region, 128 * 128);
+    slot = max(slot, (int)rec::kv_fp16_bytes(D));
+  }
+  (void)QB;
+  q_region = (q_region + 1023) & ~1023;
+  const int fixed = q_region + p_region + D * 4 + (int)sizeof(Barriers) + 128;
+  const int budget = 112 * 1024;  // two CTAs per SM
+  int nslot = (budget - fixed) / slot;
+  nslot = max(2, min(kMaxSlots, nslot));
+  p.nslot = nslot;
+  p.slot_bytes = slot;
+  p.q_region = q_region;
+  p.p_region = p_region;
+  const size_t smem = (size_t)fixed + (size_t)nslot * slot;
+  auto kernel = attention_kernel<D>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return ANEMOI_SM100_ELAUNCH;
+  kernel<<<dim3(tiles, p.s.heads), kThreads, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+int check_ops(const anemoi_sm100_shape& s, const anemoi_sm100_operands& o, bool dense_prefix) {
+  if (s.has_int8 && (!o.q_int8 || !o.kv_int8 || !o.q_int8_scale || !o.k_int8_scale || !o.v_e4m3_scale))
+    return ANEMOI_SM100_EINVAL;
+  if (dense_prefix) return s.has_int8 ? ANEMOI_SM100_OK : ANEMOI_SM100_EINVAL;
+  if (s.has_fp16 && (!o.q_fp16 || !o.kv_fp16)) return ANEMOI_SM100_EINVAL;
+  if (s.has_nvfp4 && (!o.q_nvfp4 || !o.kv_nvfp4)) return ANEMOI_SM100_EINVAL;
+  return ANEMOI_SM100_OK;
+}
+
+}  // namespace
+
+extern "C" int anemoi_sm100_attention(const anemoi_sm100_shape* shape,
+                                      const anemoi_sm100_operands* ops, const int32_t* row_offset,
+                                      const int32_t* row_counts, const int32_t* stage_ids,
+                                      int64_t list_capacity, const int32_t* valid_k,
+                                      void* out_packed, int32_t* status, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !ops || !row_offset || !row_counts ||
+      !stage_ids || !valid_k || !out_packed || !status || list_capacity <= 0)
+    return ANEMOI_SM100_EINVAL;
+  if (check_ops(*shape, *ops, false) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
+  AttnParams p{};
+  p.s = *shape;
+  p.o = *ops;
+  p.row_offset = row_offset;
+  p.row_counts = row_counts;
+  p.stage_ids = stage_ids;
+  p.capacity = list_capacity;
+  p.valid_k = valid_k;
+  p.out = static_cast<__half*>(out_packed);
+  p.status = status;
+  p.dense_prefix = 0;
+  p.stages = rec::stages(*shape);
+  p.q_tiles_int8 = shape->video_blocks + rec::prefix_query_tiles(*shape);
+  p.out_rows = shape->video_blocks * shape->query_block;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return shape->head_dim == 64 ? launch<64>(p, shape->video_blocks, st)
+                               : launch<128>(p, shape->video_blocks, st);
+}
+
+extern "C" int anemoi_sm100_prefix_attention(const anemoi_sm100_shape* shape,
+                                             const anemoi_sm100_operands* ops,
+                                             const int32_t* valid_k, void* out_prefix,
+                                             int32_t* status, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !ops || !valid_k || !out_prefix || !status)
+    return ANEMOI_SM100_EINVAL;
+  if (!shape->has_prefix_query_int8 || shape->prefix_tokens == 0) return ANEMOI_SM100_EINVAL;
+  if (check_ops(*shape, *ops, true) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
+  AttnParams p{};
+  p.s = *shape;
+  p.o = *ops;
+  p.valid_k = valid_k;
+  p.out = static_cast<__half*>(out_prefix);
+  p.status = status;
+  p.dense_prefix = 1;
+  p.stages = rec::stages(*shape);
+  const int tiles = rec::prefix_query_tiles(*shape);
+  p.q_tiles_int8 = shape->video_blocks + tiles;
+  p.out_rows = tiles * shape->query_block;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return shape->head_dim == 64 ? launch<64>(p, tiles, st) : launch<128>(p, tiles, st);
+}

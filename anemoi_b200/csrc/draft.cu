@@ -1,0 +1,184 @@
+// Draft probability: pooled-QK logits (fp32 accumulate, rounded to fp16), row
+// softmax in fp32, optional mean/max blend, fp16 result [H][R][R].
+//
+// Reference: csrc/attention/cuda/sm120/h3_draft_probability.cu:131-222 (softmax
+// and blend) and :427-465 (cuBLAS pooled GEMM, fp16 logits).  The reference
+// leaves the accumulation order to cuBLAS and uses a fast-math expf, so its own
+// map is only reproducible to ~5e-4; the routing that follows ranks these values
+// globally, so here every operation is fixed and individually rounded:
+//   dot     acc = fma(q[c], k[c], acc) for c = 0..D-1 (products of fp16 values are
+//           exact in fp32, so this equals a separately rounded add)
+//   logit   f16_rn(acc * f32(1/sqrt(D)))
+//   exp     y = max(t*log2e, -125); n = rint(y); f = y - n;
+//           p = Horner degree 7 of 2^f with rounded multiplies and adds; e = p * 2^n
+//   sum     lane l adds columns l, l+32, ... ascending; lanes are folded with an
+//           xor butterfly 16, 8, 4, 2, 1
+//   prob    f16_rn(e * (1/sum)), IEEE reciprocal; blend f16_rn((1-w)*pm + w*px)
+// A CPU restatement with the same sequence reproduces the map bit for bit.
+#include <cuda_fp16.h>
+
+#include "records.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kChunk = 64;
+constexpr int kMaxBlocks = 4096;  // rows per head the shared-memory row buffers are sized for
+
+__device__ __forceinline__ float exp_canonical(float t) {
+  const float y = fmaxf(__fmul_rn(t, __int_as_float(0x3fb8aa3b)), -125.0f);
+  const float n = rintf(y);
+  const float f = __fsub_rn(y, n);
+  float p = __int_as_float(0x377fe5fe);
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x39218489));
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x3aaec3ff));
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x3c1d955b));
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x3d635847));
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x3e75fdf0));
+  p = __fadd_rn(__fmul_rn(p, f), __int_as_float(0x3f317218));
+  p = __fadd_rn(__fmul_rn(p, f), 1.0f);
+  return __fmul_rn(p, __int_as_float((static_cast<int>(n) + 127) << 23));
+}
+
+template <int D>
+__device__ __forceinline__ void row_logits(const __half* q_pool, const __half* k_pool, int head,
+                                           int R, int row0, __half* kc, float* qs, __half* lg,
+                                           int lg_stride) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = row0 + warp;
+  const float scale = D == 64 ? 0.125f : __int_as_float(0x3db504f3);
+  // stage this CTA's query pools as floats
+  for (int idx = threadIdx.x; idx < kWarps * D; idx += kWarps * 32) {
+    const int r = row0 + idx / D;
+    qs[idx] = r < R ? __half2float(q_pool[((int64_t)head * R + r) * D + idx % D]) : 0.0f;
+  }
+  for (int c0 = 0; c0 < R; c0 += kChunk) {
+    __syncthreads();
+    // key pools of columns [c0, c0 + kChunk) transposed to [channel][column]
+    for (int idx = threadIdx.x; idx < kChunk * (D / 8); idx += kWarps * 32) {
+      const int col = idx / (D / 8), c8 = idx % (D / 8);
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (c0 + col < R)
+        raw = __ldg(reinterpret_cast<const uint4*>(k_pool + ((int64_t)head * R + c0 + col) * D) + c8);
+      const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kc[(c8 * 8 + i) * kChunk + col] = h[i];
+    }
+    __syncthreads();
+    float acc0 = 0.0f, acc1 = 0.0f;
+    const float* qrow = qs + warp * D;
+#pragma unroll 8
+    for (int c = 0; c < D; ++c) {
+      const float qv = qrow[c];
+      acc0 = __fmaf_rn(qv, __half2float(kc[c * kChunk + lane]), acc0);
+      acc1 = __fmaf_rn(qv, __half2float(kc[c * kChunk + lane + 32]), acc1);
+    }
+    if (c0 + lane < R) lg[warp * lg_stride + c0 + lane] = __float2half_rn(__fmul_rn(acc0, scale));
+    if (c0 + lane + 32 < R)
+      lg[warp * lg_stride + c0 + lane + 32] = __float2half_rn(__fmul_rn(acc1, scale));
+  }
+  (void)row;
+  __syncwarp();
+}
+
+// max and 1/sum of one row held in shared memory (warp-collective).
+__device__ __forceinline__ void row_stats(const __half* lg, int R, float& mx, float& inv) {
+  const int lane = threadIdx.x & 31;
+  float m = -INFINITY;
+  for (int j = lane; j < R; j += 32) m = fmaxf(m, __half2float(lg[j]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  float s = 0.0f;
+  for (int j = lane; j < R; j += 32) s = __fadd_rn(s, exp_canonical(__fsub_rn(__half2float(lg[j]), m)));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
+  mx = m;
+  inv = __fdiv_rn(1.0f, s);
+}
+
+template <int D, bool kBlend>
+__global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool,
+                                                            const __half* k_pool,
+                                                            const __half* q_max, const __half* k_max,
+                                                            float w, int R, __half* prob) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const int lg_stride = (R + 7) & ~7;
+  __half* kc = reinterpret_cast<__half*>(smem_raw);                 // [D][kChunk]
+  float* qs = reinterpret_cast<float*>(kc + D * kChunk);            // [kWarps][D]
+  __half* lg = reinterpret_cast<__half*>(qs + kWarps * D);          // [kWarps][lg_stride]
+  __half* lgx = lg + kWarps * lg_stride;                            // blend only
+  const int head = blockIdx.y, row0 = blockIdx.x * kWarps;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = row0 + warp;
+
+  row_logits<D>(q_pool, k_pool, head, R, row0, kc, qs, lg, lg_stride);
+  if (kBlend) {
+    __syncthreads();
+    row_logits<D>(q_max, k_max, head, R, row0, kc, qs, lgx, lg_stride);
+  }
+  if (row >= R) return;
+  const __half* mine = lg + warp * lg_stride;
+  float m, inv;
+  row_stats(mine, R, m, inv);
+  __half* out = prob + ((int64_t)head * R + row) * R;
+  if (!kBlend) {
+    for (int j = lane; j < R; j += 32)
+      out[j] = __float2half_rn(__fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv));
+  } else {
+    const __half* minex = lgx + warp * lg_stride;
+    float mxx, invx;
+    row_stats(minex, R, mxx, invx);
+    const float wm = __fsub_rn(1.0f, w);
+    for (int j = lane; j < R; j += 32) {
+      const float pm = __fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv);
+      const float px = __fmul_rn(exp_canonical(__fsub_rn(__half2float(minex[j]), mxx)), invx);
+      out[j] = __float2half_rn(__fadd_rn(__fmul_rn(wm, pm), __fmul_rn(w, px)));
+    }
+  }
+}
+
+template <int D, bool kBlend>
+int launch(const __half* qp, const __half* kp, const __half* qx, const __half* kx, float w, int R,
+           int H, __half* prob, cudaStream_t st) {
+  const int lg_stride = (R + 7) & ~7;
+  const size_t smem = (size_t)D * kChunk * 2 + (size_t)kWarps * D * 4 +
+                      (size_t)kWarps * lg_stride * 2 * (kBlend ? 2 : 1);
+  auto kernel = draft_kernel<D, kBlend>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return ANEMOI_SM100_ELAUNCH;
+  dim3 grid((R + kWarps - 1) / kWarps, H);
+  kernel<<<grid, kWarps * 32, smem, st>>>(qp, kp, qx, kx, w, R, prob);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+}  // namespace
+
+extern "C" int anemoi_sm100_draft_probability(const anemoi_sm100_shape* shape, const void* q_pool,
+                                              const void* k_pool, const void* q_max_pool,
+                                              const void* k_max_pool, float maxpool_weight,
+                                              void* probability, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !q_pool || !k_pool || !probability)
+    return ANEMOI_SM100_EINVAL;
+  if (!(maxpool_weight >= 0.0f && maxpool_weight <= 1.0f)) return ANEMOI_SM100_EINVAL;
+  if (maxpool_weight != 0.0f && (!q_max_pool || !k_max_pool)) return ANEMOI_SM100_EINVAL;
+  const int R = shape->video_blocks, H = shape->heads, D = shape->head_dim;
+  if (R > kMaxBlocks) return ANEMOI_SM100_ELIMIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half* qp = static_cast<const __half*>(q_pool);
+  const __half* kp = static_cast<const __half*>(k_pool);
+  const __half* qx = static_cast<const __half*>(q_max_pool);
+  const __half* kx = static_cast<const __half*>(k_max_pool);
+  __half* prob = static_cast<__half*>(probability);
+  if (maxpool_weight == 1.0f) {  // max pools only
+    qp = qx;
+    kp = kx;
+    maxpool_weight = 0.0f;
+  }
+  const bool blend = maxpool_weight != 0.0f;
+  if (D == 64)
+    return blend ? launch<64, true>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st)
+                 : launch<64, false>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st);
+  return blend ? launch<128, true>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st)
+               : launch<128, false>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st);
+}

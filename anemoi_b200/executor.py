@@ -1,0 +1,244 @@
+"""Orchestration of one ``anemoi_attention`` call on a B200.
+
+Follows the reference's executor (anemoi/layers/attention/mpa/executor.py):
+``execute_ragged_attention`` (:1227-1295) dispatches on the device capability -
+here only (10, 0) is accepted - and ``sm100_ragged_attention`` walks the same
+steps as ``sm120_ragged_h3_attention`` (:876-1224): validate, resolve phases,
+slot tables (cached), prepare operands, draft probability, route, attention
+phases, prefix rows on a side stream, assembly.  No host synchronisation happens
+on the path.  The public path pins the same options as the reference: mean-pool
+draft map, no diag-Jensen term, no anchors, no MXFP8 cell.
+"""
+
+from __future__ import annotations
+
+import math
+from functools import lru_cache
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .layout import materialize_ragged_2d_layout
+from .routing import PHASE_ORDER, resolve_phases, route_counts, video_phases
+
+_LAST_STATUS: dict = {}
+
+
+@lru_cache(maxsize=8)
+def _prefix_stream(device: torch.device) -> torch.cuda.Stream:
+    return torch.cuda.Stream(device=device)
+
+
+@lru_cache(maxsize=64)
+def _valid_k(device: torch.device, prefix_tokens: int, query_block: int, counts_key) -> torch.Tensor:
+    """Real keys per 64-key stage (executor.py:334-342,1052-1067 of the reference)."""
+    counts = torch.tensor(counts_key, dtype=torch.int32)
+    p = math.ceil(prefix_tokens / 64)
+    pre = torch.clamp(prefix_tokens - torch.arange(p, dtype=torch.int32) * 64, 0, 64)
+    if query_block == 128:
+        vid = torch.stack((counts.clamp_max(64), (counts - 64).clamp_min(0)), dim=-1).reshape(-1)
+    else:
+        vid = counts
+    return torch.cat((pre, vid)).to(torch.int32).to(device).contiguous()
+
+
+def make_shape(q: torch.Tensor, *, prefix_tokens: int, video_blocks: int, query_block_size: int,
+               active: tuple[str, ...], native_prefix: bool, has_maxpool: bool,
+               nvfp4_scales=(1.0, 1.0, 1.0)) -> native.Shape:
+    return native.Shape(
+        heads=q.size(2), head_dim=q.size(3), query_block=query_block_size, seq_tokens=q.size(1),
+        prefix_tokens=prefix_tokens, video_blocks=video_blocks,
+        has_nvfp4=int("nvfp4" in active), has_int8=int("int8" in active),
+        has_fp16=int("fp16" in active), has_prefix_query_int8=int(native_prefix),
+        has_maxpool=int(has_maxpool), input_is_bf16=int(q.dtype == torch.bfloat16),
+        q_global_scale=nvfp4_scales[0], k_global_scale=nvfp4_scales[1],
+        v_global_scale=nvfp4_scales[2],
+    )
+
+
+def sm100_ragged_attention(
+    q_bshd: torch.Tensor,
+    k_bshd: torch.Tensor,
+    v_bshd: torch.Tensor,
+    *,
+    prefix_tokens: int,
+    sparsity_ratio: float,
+    retained_nvfp4_ratio: float,
+    retained_int8_ratio: float,
+    retained_fp16_ratio: float,
+    video_shape: tuple[int, int, int],
+    layer: int,
+    query_block_size: int = 128,
+    prefix_kv_precision: str = "int8",
+    prefix_query_precision: str = "int8",
+    maxpool_weight: float = 0.0,
+    nvfp4_scales: tuple[float, float, float] = (1.0, 1.0, 1.0),
+    return_parts: bool = False,
+):
+    """Per-frame ragged Q64/Q128 routing and mixed-precision attention on sm_100a."""
+    if q_bshd.shape != k_bshd.shape or q_bshd.shape != v_bshd.shape:
+        raise ValueError("Q/K/V must share [1,S,H,D], D in {64,128}")
+    if (
+        q_bshd.ndim != 4
+        or q_bshd.size(0) != 1
+        or q_bshd.size(-1) not in (64, 128)
+        or q_bshd.dtype not in (torch.float16, torch.bfloat16)
+        or k_bshd.dtype != q_bshd.dtype
+        or v_bshd.dtype != q_bshd.dtype
+        or q_bshd.device.type != "cuda"
+        or k_bshd.device != q_bshd.device
+        or v_bshd.device != q_bshd.device
+    ):
+        raise ValueError("Q/K/V must be same-dtype CUDA [1,S,H,D], D in {64,128}")
+    if not (q_bshd.is_contiguous() and k_bshd.is_contiguous() and v_bshd.is_contiguous()):
+        raise ValueError("Q/K/V must be contiguous [1,S,H,D]")
+    if query_block_size not in (64, 128):
+        raise ValueError("query_block_size must be 64 or 128")
+    if isinstance(maxpool_weight, bool) or not isinstance(maxpool_weight, (int, float)):
+        raise TypeError("maxpool_weight must be a real number")
+    if not math.isfinite(float(maxpool_weight)) or not 0.0 <= float(maxpool_weight) <= 1.0:
+        raise ValueError("maxpool_weight must be finite and in [0, 1]")
+    if type(prefix_tokens) is not int or not 0 <= prefix_tokens < q_bshd.size(1):
+        raise ValueError("prefix_tokens must be nonnegative and precede the video tokens")
+    if (
+        not isinstance(video_shape, tuple)
+        or len(video_shape) != 3
+        or any(type(v) is not int or v <= 0 for v in video_shape)
+        or math.prod(video_shape) != q_bshd.size(1) - prefix_tokens
+    ):
+        raise ValueError("video_shape must match the post-prefix token count")
+
+    device = q_bshd.device
+    video = video_phases(retained_nvfp4_ratio, retained_int8_ratio, retained_fp16_ratio)
+    if prefix_query_precision not in ("int8", "fp16"):
+        raise ValueError("prefix_query_precision must be int8 or fp16")
+    native_prefix = prefix_tokens > 0 and prefix_query_precision == "int8" and "int8" in video
+    active, prefix_phase = resolve_phases(video, prefix_tokens, prefix_kv_precision)
+
+    frames, height, width = video_shape
+    current = torch.cuda.current_stream(device)
+    side = _prefix_stream(device)
+    prefix_out = None
+    if prefix_tokens and not native_prefix:
+        # dense attention of the prefix rows on the caller's tensors, as the reference does
+        side.wait_stream(current)
+        with torch.cuda.stream(side):
+            prefix_out = F.scaled_dot_product_attention(
+                q_bshd[:, :prefix_tokens].permute(0, 2, 1, 3),
+                k_bshd.permute(0, 2, 1, 3),
+                v_bshd.permute(0, 2, 1, 3),
+                dropout_p=0.0,
+                is_causal=False,
+            )[0].contiguous()
+
+    layout = materialize_ragged_2d_layout(device, frames=frames, height=height, width=width,
+                                          logical_block=query_block_size)
+    blocks = layout.video_blocks
+    shape = make_shape(q_bshd, prefix_tokens=prefix_tokens, video_blocks=blocks,
+                       query_block_size=query_block_size, active=active,
+                       native_prefix=native_prefix, has_maxpool=maxpool_weight != 0.0,
+                       nvfp4_scales=nvfp4_scales)
+    store = native.allocate_operands(shape, device)
+    native.prepare(shape, q_bshd, k_bshd, v_bshd, layout.indices, layout.counts, store)
+    valid_k = _valid_k(device, prefix_tokens, query_block_size, _counts_key(layout))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    if native_prefix:
+        side.wait_stream(current)
+        with torch.cuda.stream(side):
+            prefix_out = native.prefix_attention(shape, store, valid_k, status)
+            for t in store.buffers.values():
+                if t is not None:
+                    t.record_stream(side)
+            valid_k.record_stream(side)
+            status.record_stream(side)
+
+    prob = native.draft_probability(shape, store, float(maxpool_weight))
+    n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=float(sparsity_ratio),
+                               nvfp4_ratio=float(retained_nvfp4_ratio),
+                               int8_ratio=float(retained_int8_ratio),
+                               fp16_ratio=float(retained_fp16_ratio))
+    phase_index = -1 if prefix_phase is None else PHASE_ORDER.index(prefix_phase)
+    lists = native.route(shape, prob, n16, n8, n4, phase_index)
+    packed = native.attention(shape, store, lists, valid_k, status)
+
+    current.wait_stream(side)
+    if prefix_out is not None:
+        prefix_out.record_stream(current)
+    out = native.assemble(shape, prefix_out, packed, layout.inverse, lists.row_counts, q_bshd.dtype)
+    _LAST_STATUS[device] = status
+    if return_parts:
+        return out, dict(shape=shape, store=store, prob=prob, lists=lists, packed=packed,
+                         prefix_out=prefix_out, valid_k=valid_k, budgets=(n16, n8, n4),
+                         layout=layout, status=status)
+    return out
+
+
+def _counts_key(layout) -> tuple:
+    key = getattr(layout, "_counts_key", None)
+    if key is None:
+        key = tuple(int(c) for c in layout.counts.cpu().tolist())
+        object.__setattr__(layout, "_counts_key", key)
+    return key
+
+
+def last_status(device=None) -> int:
+    """Synchronise and return the device status word of the latest call (0 = clean).
+
+    A non-zero value means a bounded wait inside the attention kernel gave up; the
+    output of that call is not valid.
+    """
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    status = _LAST_STATUS.get(torch.device(device))
+    return 0 if status is None else int(status.item())
+
+
+def execute_ragged_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    prefix_tokens: int,
+    video_shape: tuple[int, int, int],
+    layer: int,
+    query_block_size: int,
+    sparsity_ratio: float,
+    nvfp4_ratio: float,
+    int8_ratio: float,
+    fp16_ratio: float,
+    prefix_kv_precision: str,
+    prefix_query_precision: str,
+    maxpool_weight: float = 0.0,
+    nvfp4_scales: tuple[float, float, float] = (1.0, 1.0, 1.0),
+) -> torch.Tensor:
+    """Dispatch the stable routing configuration to the sm_100a backend."""
+    if query.device.type != "cuda":
+        raise RuntimeError("Anemoi attention requires an SM100 (B200) CUDA device")
+    capability = tuple(torch.cuda.get_device_capability(query.device))
+    if capability != (10, 0):
+        raise RuntimeError("Anemoi attention requires SM100 (B200)")
+    phases = video_phases(nvfp4_ratio, int8_ratio, fp16_ratio)
+    if prefix_tokens and prefix_query_precision == "int8" and "int8" not in phases:
+        raise RuntimeError("prefix-query INT8 requires an active INT8 phase")
+    return sm100_ragged_attention(
+        query,
+        key,
+        value,
+        prefix_tokens=prefix_tokens,
+        sparsity_ratio=sparsity_ratio,
+        retained_nvfp4_ratio=nvfp4_ratio,
+        retained_int8_ratio=int8_ratio,
+        retained_fp16_ratio=fp16_ratio,
+        video_shape=video_shape,
+        layer=layer,
+        query_block_size=query_block_size,
+        prefix_kv_precision=prefix_kv_precision,
+        prefix_query_precision=prefix_query_precision,
+        maxpool_weight=maxpool_weight,
+        nvfp4_scales=nvfp4_scales,
+    )
+
+
+__all__ = ["execute_ragged_attention", "sm100_ragged_attention", "last_status"]

@@ -1,0 +1,282 @@
+"""ctypes binding of ``libanemoi_sm100.so`` (the C ABI declared in include/anemoi_sm100.h).
+
+Plays the role of the reference's backend wrappers over ``torch.ops.mixed_attention.*``
+(anemoi/layers/attention/mpa/backends/sm120_q64.py, sm120_q128.py, sm89_k64.py and
+mpa/build_identity.py): one Python function per native entry point, marshaling
+tensors to raw device pointers on the current CUDA stream.  There is no fallback:
+a missing library raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+LIBRARY_NAME = "libanemoi_sm100.so"
+
+(BUF_Q_FP16, BUF_KV_FP16, BUF_Q_INT8, BUF_KV_INT8, BUF_Q_NVFP4, BUF_KV_NVFP4, BUF_Q_INT8_SCALE,
+ BUF_K_INT8_SCALE, BUF_V_E4M3_SCALE, BUF_V_AMAX, BUF_POOL, BUF_COUNT) = range(12)
+
+ERRORS = {-1: "invalid argument", -2: "CUDA launch failure", -3: "size beyond a documented limit"}
+
+
+class Shape(C.Structure):
+    _fields_ = [
+        ("heads", C.c_int32), ("head_dim", C.c_int32), ("query_block", C.c_int32),
+        ("seq_tokens", C.c_int32), ("prefix_tokens", C.c_int32), ("video_blocks", C.c_int32),
+        ("has_nvfp4", C.c_int32), ("has_int8", C.c_int32), ("has_fp16", C.c_int32),
+        ("has_prefix_query_int8", C.c_int32), ("has_maxpool", C.c_int32),
+        ("input_is_bf16", C.c_int32),
+        ("q_global_scale", C.c_float), ("k_global_scale", C.c_float), ("v_global_scale", C.c_float),
+    ]
+
+    @property
+    def prefix_stages(self) -> int:
+        return math.ceil(self.prefix_tokens / 64)
+
+    @property
+    def stages(self) -> int:
+        return self.prefix_stages + self.video_blocks * (self.query_block // 64)
+
+    @property
+    def prefix_query_tiles(self) -> int:
+        if not self.has_prefix_query_int8:
+            return 0
+        return math.ceil(self.prefix_tokens / self.query_block)
+
+
+class Operands(C.Structure):
+    _fields_ = [(name, C.c_void_p) for name in (
+        "q_fp16", "kv_fp16", "q_int8", "kv_int8", "q_nvfp4", "kv_nvfp4", "q_int8_scale",
+        "k_int8_scale", "v_e4m3_scale", "v_amax", "q_pool", "k_pool", "q_max_pool", "k_max_pool")]
+
+
+@lru_cache(maxsize=1)
+def library() -> C.CDLL:
+    """Load the in-tree shared library; raise if it has not been built."""
+    path = Path(__file__).resolve().parent / LIBRARY_NAME
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m anemoi_b200.build` "
+            "(nvcc, sm_100a). There is no fallback path."
+        )
+    lib = C.CDLL(str(path))
+    P, I32, I64, F = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+    SP, OP = C.POINTER(Shape), C.POINTER(Operands)
+    signatures = {
+        "anemoi_sm100_arch": (C.c_int, []),
+        "anemoi_sm100_operand_bytes": (I64, [SP, C.c_int]),
+        "anemoi_sm100_prepare": (C.c_int, [SP, P, P, P, P, P, OP, P]),
+        "anemoi_sm100_draft_probability": (C.c_int, [SP, P, P, P, P, F, P, P]),
+        "anemoi_sm100_route_scratch_bytes": (I64, [SP]),
+        "anemoi_sm100_route_list_capacity": (I64, [SP, I64, I64, I64, C.c_int]),
+        "anemoi_sm100_route": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, I64, P, P, P, I64, P]),
+        "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
+        "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
+        "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
+        "anemoi_sm100_pack_qkv": (C.c_int, [P, P, P, P, I64, I32, I32, I32, C.POINTER(I64), P]),
+        "anemoi_sm100_merge_heads": (C.c_int, [P, P, I64, I32, I32, I32, P]),
+    }
+    for name, (restype, argtypes) in signatures.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    if lib.anemoi_sm100_arch() != 100:
+        raise RuntimeError("libanemoi_sm100.so was not built for sm_100a")
+    return lib
+
+
+EXPORTED = (
+    "anemoi_sm100_arch", "anemoi_sm100_operand_bytes", "anemoi_sm100_prepare",
+    "anemoi_sm100_draft_probability", "anemoi_sm100_route_scratch_bytes",
+    "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_attention",
+    "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
+    "anemoi_sm100_merge_heads",
+)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed: {ERRORS.get(code, code)}")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+@dataclass
+class OperandStore:
+    """Device buffers behind an ``Operands`` struct (kept alive with it)."""
+
+    shape: Shape
+    buffers: dict
+    struct: Operands
+
+    def raw(self, name: str) -> torch.Tensor:
+        return self.buffers[name]
+
+
+def allocate_operands(shape: Shape, device) -> OperandStore:
+    lib = library()
+
+    def nbytes(which: int) -> int:
+        n = lib.anemoi_sm100_operand_bytes(C.byref(shape), which)
+        if n < 0:
+            raise RuntimeError("invalid attention shape")
+        return int(n)
+
+    buffers: dict[str, torch.Tensor | None] = {}
+
+    def alloc(name: str, which: int, dtype=torch.uint8):
+        n = nbytes(which)
+        if n == 0:
+            buffers[name] = None
+            return
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        buffers[name] = torch.empty(n // itemsize, dtype=dtype, device=device)
+
+    alloc("q_fp16", BUF_Q_FP16)
+    alloc("kv_fp16", BUF_KV_FP16)
+    alloc("q_int8", BUF_Q_INT8)
+    alloc("kv_int8", BUF_KV_INT8)
+    alloc("q_nvfp4", BUF_Q_NVFP4)
+    alloc("kv_nvfp4", BUF_KV_NVFP4)
+    alloc("q_int8_scale", BUF_Q_INT8_SCALE, torch.float32)
+    alloc("k_int8_scale", BUF_K_INT8_SCALE, torch.float32)
+    alloc("v_e4m3_scale", BUF_V_E4M3_SCALE, torch.float32)
+    alloc("v_amax", BUF_V_AMAX, torch.float32)
+    pool = (shape.heads, shape.video_blocks, shape.head_dim)
+    buffers["q_pool"] = torch.empty(pool, dtype=torch.float16, device=device)
+    buffers["k_pool"] = torch.empty(pool, dtype=torch.float16, device=device)
+    if shape.has_maxpool:
+        buffers["q_max_pool"] = torch.empty(pool, dtype=torch.float16, device=device)
+        buffers["k_max_pool"] = torch.empty(pool, dtype=torch.float16, device=device)
+    else:
+        buffers["q_max_pool"] = buffers["k_max_pool"] = None
+    struct = Operands(**{k: (None if v is None else v.data_ptr()) for k, v in buffers.items()})
+    return OperandStore(shape=shape, buffers=buffers, struct=struct)
+
+
+def prepare(shape: Shape, q, k, v, indices, counts, store: OperandStore) -> None:
+    """Fill the operand store from raw ``[1, S, H, D]`` Q/K/V (see anemoi_sm100_prepare)."""
+    _check(library().anemoi_sm100_prepare(C.byref(shape), _ptr(q), _ptr(k), _ptr(v), _ptr(indices),
+                                          _ptr(counts), C.byref(store.struct), _stream(q.device)),
+           "anemoi_sm100_prepare")
+
+
+def draft_probability(shape: Shape, store: OperandStore, maxpool_weight: float) -> torch.Tensor:
+    r = shape.video_blocks
+    prob = torch.empty((shape.heads, r, r), dtype=torch.float16, device=store.buffers["q_pool"].device)
+    b = store.buffers
+    _check(library().anemoi_sm100_draft_probability(
+        C.byref(shape), _ptr(b["q_pool"]), _ptr(b["k_pool"]), _ptr(b["q_max_pool"]),
+        _ptr(b["k_max_pool"]), float(maxpool_weight), _ptr(prob), _stream(prob.device)),
+        "anemoi_sm100_draft_probability")
+    return prob
+
+
+@dataclass
+class RouteLists:
+    row_offset: torch.Tensor   # int32 [H, R]
+    row_counts: torch.Tensor   # int32 [H, R, 4]
+    stage_ids: torch.Tensor    # int32 [H, capacity]
+    capacity: int
+
+
+def route(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_phase: int) -> RouteLists:
+    lib = library()
+    dev = prob.device
+    h, r = shape.heads, shape.video_blocks
+    scratch = torch.empty(int(lib.anemoi_sm100_route_scratch_bytes(C.byref(shape))), dtype=torch.uint8,
+                          device=dev)
+    if not shape.prefix_tokens:
+        prefix_phase = -1
+    cap = int(lib.anemoi_sm100_route_list_capacity(C.byref(shape), n16, n8, n4, prefix_phase))
+    lists = RouteLists(
+        row_offset=torch.empty((h, r), dtype=torch.int32, device=dev),
+        row_counts=torch.empty((h, r, 4), dtype=torch.int32, device=dev),
+        stage_ids=torch.empty((h, max(cap, 1)), dtype=torch.int32, device=dev),
+        capacity=max(cap, 1),
+    )
+    _check(lib.anemoi_sm100_route(C.byref(shape), _ptr(prob), n16, n8, n4, prefix_phase,
+                                  _ptr(scratch), scratch.numel(), _ptr(lists.row_offset),
+                                  _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,
+                                  _stream(dev)), "anemoi_sm100_route")
+    return lists
+
+
+def attention(shape: Shape, store: OperandStore, lists: RouteLists, valid_k: torch.Tensor,
+              status: torch.Tensor) -> torch.Tensor:
+    dev = valid_k.device
+    out = torch.empty((shape.heads, shape.video_blocks * shape.query_block, shape.head_dim),
+                      dtype=torch.float16, device=dev)
+    _check(library().anemoi_sm100_attention(
+        C.byref(shape), C.byref(store.struct), _ptr(lists.row_offset), _ptr(lists.row_counts),
+        _ptr(lists.stage_ids), lists.capacity, _ptr(valid_k), _ptr(out), _ptr(status),
+        _stream(dev)), "anemoi_sm100_attention")
+    return out
+
+
+def prefix_attention(shape: Shape, store: OperandStore, valid_k: torch.Tensor,
+                     status: torch.Tensor) -> torch.Tensor:
+    dev = valid_k.device
+    rows = shape.prefix_query_tiles * shape.query_block
+    out = torch.empty((shape.heads, rows, shape.head_dim), dtype=torch.float16, device=dev)
+    _check(library().anemoi_sm100_prefix_attention(
+        C.byref(shape), C.byref(store.struct), _ptr(valid_k), _ptr(out), _ptr(status),
+        _stream(dev)), "anemoi_sm100_prefix_attention")
+    return out
+
+
+def assemble(shape: Shape, prefix_out: torch.Tensor | None, out_packed: torch.Tensor,
+             inverse: torch.Tensor, row_counts: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    dev = out_packed.device
+    out = torch.empty((1, shape.seq_tokens, shape.heads, shape.head_dim), dtype=dtype, device=dev)
+    caller = 0
+    rows = 0
+    if prefix_out is not None:
+        rows = prefix_out.shape[1]
+        if prefix_out.dtype not in (torch.float16, dtype):
+            raise TypeError("prefix rows must be fp16 or the caller's dtype")
+        caller = int(prefix_out.dtype != torch.float16)
+    _check(library().anemoi_sm100_assemble(
+        C.byref(shape), _ptr(prefix_out), rows, caller, _ptr(out_packed), _ptr(inverse),
+        _ptr(row_counts), _ptr(out), _stream(dev)), "anemoi_sm100_assemble")
+    return out
+
+
+def pack_qkv_destination_major(q, k, v, world: int) -> torch.Tensor:
+    """``(rows, heads, D)`` x3 (strided views allowed) -> ``(world, rows, heads/world, 3*D)``."""
+    rows, heads, d = q.shape
+    if heads % world:
+        raise ValueError(f"heads ({heads}) must divide the Ulysses degree ({world})")
+    if not (q.shape == k.shape == v.shape and q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k, v must share shape and dtype")
+    if q.element_size() != 2 or any(t.stride(-1) != 1 for t in (q, k, v)):
+        raise ValueError("pack_qkv needs 16-bit tensors with a contiguous head dimension")
+    out = torch.empty((world, rows, heads // world, 3 * d), dtype=q.dtype, device=q.device)
+    strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
+    _check(library().anemoi_sm100_pack_qkv(_ptr(q), _ptr(k), _ptr(v), _ptr(out), rows, heads, d,
+                                           world, strides, _stream(q.device)),
+           "anemoi_sm100_pack_qkv")
+    return out
+
+
+def merge_heads(x: torch.Tensor) -> torch.Tensor:
+    """``(world, rows, heads_local, D)`` contiguous -> ``(rows, world*heads_local, D)``."""
+    world, rows, hl, d = x.shape
+    if not x.is_contiguous() or x.element_size() != 2:
+        raise ValueError("merge_heads needs a contiguous 16-bit tensor")
+    out = torch.empty((rows, world * hl, d), dtype=x.dtype, device=x.device)
+    _check(library().anemoi_sm100_merge_heads(_ptr(x), _ptr(out), rows, world, hl, d,
+                                              _stream(x.device)), "anemoi_sm100_merge_heads")
+    return out

@@ -1,0 +1,179 @@
+/* C ABI of the B200 (sm_100a) sparse mixed-precision attention path.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every
+ * entry point is asynchronous on `stream` (a cudaStream_t passed as void*),
+ * allocates nothing unless stated, never synchronises the host, and returns 0
+ * or a negative ANEMOI_SM100_E* code before anything is launched.  All device
+ * pointers must belong to the current device.  Batch size is 1, as in the
+ * reference (anemoi/layers/attention/mpa/executor.py:903-919).
+ *
+ * The functions replace, one for one or fused, the custom operators the
+ * reference registers in csrc/attention/cuda/sm120/bindings.cpp:9-176 and
+ * csrc/attention/cuda/sm89/bindings.cpp (shared pack / assemble operators).
+ */
+#ifndef ANEMOI_SM100_H_
+#define ANEMOI_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  ANEMOI_SM100_OK = 0,
+  ANEMOI_SM100_EINVAL = -1,   /* bad shape, flag or null pointer */
+  ANEMOI_SM100_ELAUNCH = -2,  /* the CUDA runtime refused a launch */
+  ANEMOI_SM100_ELIMIT = -3    /* size beyond a documented maximum */
+};
+
+/* Geometry and active precision cells of one call. */
+typedef struct anemoi_sm100_shape {
+  int32_t heads;            /* H (heads held by this GPU) */
+  int32_t head_dim;         /* D: 64 or 128 */
+  int32_t query_block;      /* QB: 64 or 128 (also the logical key block) */
+  int32_t seq_tokens;       /* S = prefix_tokens + video tokens */
+  int32_t prefix_tokens;
+  int32_t video_blocks;     /* R = frames * blocks per frame */
+  int32_t has_nvfp4;        /* cells that need operands (video phases + prefix phase) */
+  int32_t has_int8;
+  int32_t has_fp16;
+  int32_t has_prefix_query_int8; /* prefix queries run through the INT8 cell */
+  int32_t has_maxpool;
+  int32_t input_is_bf16;    /* raw Q/K/V dtype: 1 bf16, 0 fp16 */
+  float q_global_scale;     /* NVFP4 tensor-level scales (NVFP4Calibration) */
+  float k_global_scale;
+  float v_global_scale;
+} anemoi_sm100_shape;
+
+/* Operand store filled by anemoi_sm100_prepare and read by the attention
+ * kernels.  Tiles are kept in the order the tensor core reads them from shared
+ * memory (8 rows x 16 bytes core matrices, no swizzle), one contiguous record
+ * per (head, query tile) or (head, 64-key stage), so a single bulk copy lands a
+ * ready operand.  Pointers of inactive cells may be null.  Sizes in bytes come
+ * from anemoi_sm100_operand_bytes(). */
+typedef struct anemoi_sm100_operands {
+  void* q_fp16;     /* [H][R] records: Q tile QBxD fp16 */
+  void* kv_fp16;    /* [H][stages] records: K tile 64xD fp16 | V tile 64xD fp16 */
+  void* q_int8;     /* [H][R + prefix query tiles] records: Q tile QBxD s8 */
+  void* kv_int8;    /* [H][stages] records: K tile 64xD s8 | V tile Dx64 e4m3 */
+  void* q_nvfp4;    /* [H][R] records: Q tile QBxD e2m1 | scale bytes */
+  void* kv_nvfp4;   /* [H][stages] records: K e2m1 | V^T e2m1 | K scales | V scales */
+  float* q_int8_scale;   /* [H][R + prefix query tiles] */
+  float* k_int8_scale;   /* [H][stages] */
+  float* v_e4m3_scale;   /* [H][D] = amax/2.25 */
+  float* v_amax;         /* [H][D] scratch of the V amax pre-pass (int8 cell) */
+  void* q_pool;          /* [H][R][D] fp16 mean pools */
+  void* k_pool;
+  void* q_max_pool;      /* [H][R][D] fp16 max pools (has_maxpool) */
+  void* k_max_pool;
+} anemoi_sm100_operands;
+
+enum {
+  ANEMOI_SM100_BUF_Q_FP16 = 0, ANEMOI_SM100_BUF_KV_FP16, ANEMOI_SM100_BUF_Q_INT8,
+  ANEMOI_SM100_BUF_KV_INT8, ANEMOI_SM100_BUF_Q_NVFP4, ANEMOI_SM100_BUF_KV_NVFP4,
+  ANEMOI_SM100_BUF_Q_INT8_SCALE, ANEMOI_SM100_BUF_K_INT8_SCALE, ANEMOI_SM100_BUF_V_E4M3_SCALE,
+  ANEMOI_SM100_BUF_V_AMAX, ANEMOI_SM100_BUF_POOL, ANEMOI_SM100_BUF_COUNT
+};
+
+/* Library identity: returns 100 (the sm_ architecture this build targets). */
+int anemoi_sm100_arch(void);
+
+/* Bytes of buffer `which` (ANEMOI_SM100_BUF_*) for `shape`; 0 if the cell is
+ * inactive; negative on a bad shape. */
+int64_t anemoi_sm100_operand_bytes(const anemoi_sm100_shape* shape, int which);
+
+/* Gather + narrow + pool + quantise in one pass over raw Q/K/V ([1,S,H,D]
+ * contiguous, bf16 or fp16).  `indices` int32 [R*QB] (slot -> video token),
+ * `counts` int32 [R] (real tokens per block).
+ * Replaces prepare_h3_sm120_operands (sm120/bindings.cpp, kernels in
+ * sm120/q128_microscaling_preparation.cu:245-803) and, for the pure FP16 cell,
+ * pack_h3_k64_qkv_fp16 + the torch pools (mpa/executor.py:83-108). */
+int anemoi_sm100_prepare(const anemoi_sm100_shape* shape, const void* q, const void* k,
+                         const void* v, const int32_t* indices, const int32_t* counts,
+                         const anemoi_sm100_operands* out, void* stream);
+
+/* Pooled-QK row softmax -> fp16 probability [H][R][R]; with 0 < w < 1 the mean
+ * and max maps are blended, w == 1 uses the max pools only.
+ * Replaces sm120_h3_draft_probability (sm120/h3_draft_probability.cu:531-670). */
+int anemoi_sm100_draft_probability(const anemoi_sm100_shape* shape, const void* q_pool,
+                                   const void* k_pool, const void* q_max_pool,
+                                   const void* k_max_pool, float maxpool_weight,
+                                   void* probability, void* stream);
+
+/* Bytes of scratch anemoi_sm100_route needs for `shape`. */
+int64_t anemoi_sm100_route_scratch_bytes(const anemoi_sm100_shape* shape);
+
+/* Entries per head of the compact stage list: (n16+n8+n4)*QB/64 + R*prefix stages
+ * (prefix stages are spliced only when prefix_phase >= 0). */
+int64_t anemoi_sm100_route_list_capacity(const anemoi_sm100_shape* shape, int64_t n16,
+                                         int64_t n8, int64_t n4, int prefix_phase);
+
+/* Global per-head top-k with precision by rank, compacted per query block into
+ * ragged 64-key stage lists.
+ *   probability  fp16 [H][R][R]
+ *   n16,n8,n4    per-head budgets (FP16, INT8, NVFP4)
+ *   prefix_phase -1 none, 0 nvfp4, 1 int8, 2 fp16: phase that carries the prefix stages
+ *   row_offset   int32 [H][R]   start of the row's list inside the head's segment
+ *   row_counts   int32 [H][R][4] stages per phase (nvfp4, int8, fp16, 0), prefix included
+ *   stage_ids    int32 [H][capacity] lists: nvfp4 stages, int8 stages, fp16 stages;
+ *                logical columns ascend inside a phase, prefix stages lead their phase
+ * Ties are broken by ascending flat index row*R+col.
+ * Replaces sm120_h3_route_precision + sm120_h3_materialize_route
+ * (sm120/h3_route_precision.cu:373-647); anchors are not supported (the public
+ * path never enables them, mpa/executor.py:1272). */
+int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* probability, int64_t n16,
+                       int64_t n8, int64_t n4, int prefix_phase, void* scratch,
+                       int64_t scratch_bytes, int32_t* row_offset, int32_t* row_counts,
+                       int32_t* stage_ids, int64_t list_capacity, void* stream);
+
+/* Block-sparse mixed-precision flash attention of the video query blocks.
+ *   valid_k      int32 [stages] real keys per stage
+ *   out_packed   fp16 [H][R*QB][D] packed row order; rows of empty lists are not written
+ *   status       int32 [1] device word, set non-zero if a bounded wait gave up
+ * Replaces sm120_q{64,128}_{fp16,int8_fp16,nvfp4_fp16,nv_int8_fp16}_attention_forward
+ * (sm120/bindings.cpp, sm120/q64_attention_host.cu). */
+int anemoi_sm100_attention(const anemoi_sm100_shape* shape, const anemoi_sm100_operands* ops,
+                           const int32_t* row_offset, const int32_t* row_counts,
+                           const int32_t* stage_ids, int64_t list_capacity,
+                           const int32_t* valid_k, void* out_packed, int32_t* status,
+                           void* stream);
+
+/* Dense INT8-cell attention of the prefix query rows over every stage.
+ *   out_prefix   fp16 [H][prefix query tiles * QB][D]
+ * Replaces sm120_q{64,128}_prefix_int8_attention_forward
+ * (sm120/q64_attention_host.cu:410-544). */
+int anemoi_sm100_prefix_attention(const anemoi_sm100_shape* shape,
+                                  const anemoi_sm100_operands* ops, const int32_t* valid_k,
+                                  void* out_prefix, int32_t* status, void* stream);
+
+/* Inverse scatter into [1,S,H,D] of the caller's dtype: prefix rows from
+ * `prefix_out` ([H][rows][D], fp16 if prefix_is_caller_dtype == 0 else the
+ * caller dtype, row stride `prefix_rows`), video rows from out_packed through
+ * `inverse` (int32 [video tokens] -> slot); query blocks whose three counts are
+ * all zero yield +0.  Replaces assemble_h3_k64_output
+ * (sm89/output_assembly.cu:219-305). */
+int anemoi_sm100_assemble(const anemoi_sm100_shape* shape, const void* prefix_out,
+                          int64_t prefix_rows, int prefix_is_caller_dtype,
+                          const void* out_packed, const int32_t* inverse,
+                          const int32_t* row_counts, void* output, void* stream);
+
+/* Ulysses relayout helpers (sequence-sharded <-> head-sharded); 16-bit elements,
+ * moved unchanged with 16-byte copies.
+ * pack : q,k,v [rows][heads][D] strided views (strides[6] = row and head stride
+ *        of q, k, v in elements, each a multiple of 8; D contiguous)
+ *        -> send [ranks][rows][heads/ranks][3*D] contiguous (destination-major)
+ * merge: recv [ranks][rows][heads_per_rank][D] -> out [rows][ranks*heads_per_rank][D]
+ * Replace the Triton kernels _pack_qkv_kernel / _merge_heads_kernel of
+ * anemoi/models/minimax_h3/solengine/models/minimax_h3/optimized/relayout.py:37-162. */
+int anemoi_sm100_pack_qkv(const void* q, const void* k, const void* v, void* send, int64_t rows,
+                          int32_t heads, int32_t head_dim, int32_t ranks, const int64_t* strides,
+                          void* stream);
+int anemoi_sm100_merge_heads(const void* recv, void* out, int64_t rows, int32_t ranks,
+                             int32_t heads_per_rank, int32_t head_dim, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANEMOI_SM100_H_ */
