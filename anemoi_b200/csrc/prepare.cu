@@ -35,6 +35,7 @@ struct PrepParams {
   const int32_t* indices;
   const int32_t* counts;
   int prefix_stages, stages, prefix_q_tiles;
+  int64_t stride[6];  // token and head stride (elements) of q, k, v
 };
 
 template <typename InT>
@@ -92,16 +93,16 @@ __device__ __forceinline__ int8_t int8_code(float x, float scale) {
 template <typename InT, int D>
 __device__ __forceinline__ void gather_tile(__half* tile, const InT* src, const PrepParams& p,
                                             int head, int rows, bool video, int first_slot,
-                                            int first_token, int valid_rows) {
+                                            int first_token, int valid_rows, int64_t token_stride,
+                                            int64_t head_stride) {
   constexpr int kVec = D / 8;
-  const int64_t row_stride = (int64_t)p.s.heads * D;
   for (int idx = threadIdx.x; idx < rows * kVec; idx += kThreads) {
     const int r = idx / kVec, c8 = idx % kVec;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (r < valid_rows) {
       const int64_t token =
           video ? (int64_t)p.s.prefix_tokens + p.indices[first_slot + r] : (int64_t)first_token + r;
-      val = load_narrow8<InT>(src + token * row_stride + (int64_t)head * D + c8 * 8);
+      val = load_narrow8<InT>(src + token * token_stride + (int64_t)head * head_stride + c8 * 8);
     }
     *reinterpret_cast<uint4*>(tile + r * (D + kPad) + c8 * 8) = val;
   }
@@ -278,7 +279,8 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
     const bool video = task < R;
     const int t = video ? task : task - (2 * R + p.prefix_stages);
     const int valid = video ? p.counts[t] : min(QB, p.s.prefix_tokens - t * QB);
-    gather_tile<InT, D>(tile, q, p, head, QB, video, t * QB, t * QB, valid);
+    gather_tile<InT, D>(tile, q, p, head, QB, video, t * QB, t * QB, valid, p.stride[0],
+                        p.stride[1]);
     __syncthreads();
     if (video) {
       __half* mean = static_cast<__half*>(p.o.q_pool) + ((int64_t)head * R + t) * D;
@@ -317,7 +319,8 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
   const int valid = video ? p.counts[b] : min(64, p.s.prefix_tokens - b * 64);
   const int64_t rec0 = (int64_t)head * p.stages + stage0;
 
-  gather_tile<InT, D>(tile, k, p, head, rows, video, b * QB, b * 64, valid);
+  gather_tile<InT, D>(tile, k, p, head, rows, video, b * QB, b * 64, valid, p.stride[2],
+                      p.stride[3]);
   __syncthreads();
   if (video) {
     __half* mean = static_cast<__half*>(p.o.k_pool) + ((int64_t)head * R + b) * D;
@@ -347,7 +350,8 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
   __syncthreads();
 
   // ---- values of the same rows ----
-  gather_tile<InT, D>(tile, v, p, head, rows, video, b * QB, b * 64, valid);
+  gather_tile<InT, D>(tile, v, p, head, rows, video, b * QB, b * 64, valid, p.stride[4],
+                      p.stride[5]);
   if (p.s.has_int8 && threadIdx.x < D) {
     const float amax =
         __half2float(__float2half_rn(p.o.v_amax[(int64_t)head * D + threadIdx.x]));
@@ -378,14 +382,16 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
 // non-negative float (integer max == float max).  `out` must be zeroed first.
 template <typename InT>
 __global__ void __launch_bounds__(256) v_amax_kernel(const InT* v, int* out, int64_t tokens,
-                                                     int row_elems, int tokens_per_block) {
+                                                     int heads, int d8, int64_t token_stride,
+                                                     int64_t head_stride, int tokens_per_block) {
   const int col8 = blockIdx.x * 256 + threadIdx.x;
-  if (col8 * 8 >= row_elems) return;
+  if (col8 >= heads * d8) return;
+  const int head = col8 / d8, c8 = col8 % d8;
   const int64_t t0 = (int64_t)blockIdx.y * tokens_per_block;
   const int64_t t1 = min(tokens, t0 + tokens_per_block);
   float m[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   for (int64_t t = t0; t < t1; ++t) {
-    uint4 raw = load_narrow8<InT>(v + t * row_elems + col8 * 8);
+    uint4 raw = load_narrow8<InT>(v + t * token_stride + head * head_stride + c8 * 8);
     const __half* h = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
     for (int i = 0; i < 8; ++i) m[i] = fmaxf(m[i], fabsf(__half2float(h[i])));
@@ -404,12 +410,12 @@ int launch(const PrepParams& p, cudaStream_t stream) {
   if (p.s.has_int8) {
     if (cudaMemsetAsync(p.o.v_amax, 0, sizeof(float) * p.s.heads * D, stream) != cudaSuccess)
       return ANEMOI_SM100_ELAUNCH;
-    const int row_elems = p.s.heads * D;
+    const int cols = p.s.heads * D / 8;
     const int tokens_per_block = 128;
-    dim3 grid((row_elems / 8 + 255) / 256, (p.s.seq_tokens + tokens_per_block - 1) / tokens_per_block);
-    v_amax_kernel<InT><<<grid, 256, 0, stream>>>(static_cast<const InT*>(p.v),
-                                                 reinterpret_cast<int*>(p.o.v_amax),
-                                                 p.s.seq_tokens, row_elems, tokens_per_block);
+    dim3 grid((cols + 255) / 256, (p.s.seq_tokens + tokens_per_block - 1) / tokens_per_block);
+    v_amax_kernel<InT><<<grid, 256, 0, stream>>>(
+        static_cast<const InT*>(p.v), reinterpret_cast<int*>(p.o.v_amax), p.s.seq_tokens,
+        p.s.heads, D / 8, p.stride[4], p.stride[5], tokens_per_block);
   }
   dim3 grid(2 * p.s.video_blocks + p.prefix_stages + p.prefix_q_tiles, p.s.heads);
   kernel<<<grid, kThreads, smem, stream>>>(p);
@@ -441,8 +447,9 @@ extern "C" int64_t anemoi_sm100_operand_bytes(const anemoi_sm100_shape* s, int w
 }
 
 extern "C" int anemoi_sm100_prepare(const anemoi_sm100_shape* shape, const void* q, const void* k,
-                                    const void* v, const int32_t* indices, const int32_t* counts,
-                                    const anemoi_sm100_operands* out, void* stream) {
+                                    const void* v, const int64_t* strides, const int32_t* indices,
+                                    const int32_t* counts, const anemoi_sm100_operands* out,
+                                    void* stream) {
   if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !q || !k || !v || !indices || !counts || !out)
     return ANEMOI_SM100_EINVAL;
   const anemoi_sm100_shape& s = *shape;
@@ -461,6 +468,10 @@ extern "C" int anemoi_sm100_prepare(const anemoi_sm100_shape* shape, const void*
   p.v = v;
   p.indices = indices;
   p.counts = counts;
+  for (int i = 0; i < 6; ++i) {
+    p.stride[i] = strides ? strides[i] : (i & 1 ? (int64_t)s.head_dim : (int64_t)s.heads * s.head_dim);
+    if (p.stride[i] <= 0 || p.stride[i] % 8) return ANEMOI_SM100_EINVAL;
+  }
   p.prefix_stages = rec::prefix_stages(s);
   p.stages = rec::stages(s);
   p.prefix_q_tiles = rec::prefix_query_tiles(s);

@@ -23,6 +23,42 @@ from .layout import materialize_ragged_2d_layout
 from .routing import PHASE_ORDER, resolve_phases, route_counts, video_phases
 
 _LAST_STATUS: dict = {}
+_STAGE_EVENTS: list | None = None
+
+
+def collect_stage_events(enable: bool) -> None:
+    """Start (or stop) recording CUDA events around each native stage of later calls."""
+    global _STAGE_EVENTS
+    _STAGE_EVENTS = [] if enable else None
+
+
+def stage_times_ms() -> dict:
+    """Per-stage device time summed over the calls recorded so far (synchronises)."""
+    torch.cuda.synchronize()
+    out: dict = {}
+    for name, start, end in _STAGE_EVENTS or []:
+        out[name] = out.get(name, 0.0) + start.elapsed_time(end)
+    return out
+
+
+class _Stage:
+    """Brackets one native stage with CUDA events on the current stream when enabled."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _STAGE_EVENTS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _STAGE_EVENTS is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            _STAGE_EVENTS.append((self.name, self.start, end))
+        return False
 
 
 @lru_cache(maxsize=8)
@@ -91,8 +127,9 @@ def sm100_ragged_attention(
         or v_bshd.device != q_bshd.device
     ):
         raise ValueError("Q/K/V must be same-dtype CUDA [1,S,H,D], D in {64,128}")
-    if not (q_bshd.is_contiguous() and k_bshd.is_contiguous() and v_bshd.is_contiguous()):
-        raise ValueError("Q/K/V must be contiguous [1,S,H,D]")
+    if any(t.stride(3) != 1 or t.stride(1) % 8 or t.stride(2) % 8 or t.data_ptr() % 16
+           for t in (q_bshd, k_bshd, v_bshd)):
+        raise ValueError("Q/K/V need a contiguous head dimension and 16-byte aligned rows")
     if query_block_size not in (64, 128):
         raise ValueError("query_block_size must be 64 or 128")
     if isinstance(maxpool_weight, bool) or not isinstance(maxpool_weight, (int, float)):
@@ -140,33 +177,40 @@ def sm100_ragged_attention(
                        native_prefix=native_prefix, has_maxpool=maxpool_weight != 0.0,
                        nvfp4_scales=nvfp4_scales)
     store = native.allocate_operands(shape, device)
-    native.prepare(shape, q_bshd, k_bshd, v_bshd, layout.indices, layout.counts, store)
+    with _Stage("prepare"):
+        native.prepare(shape, q_bshd, k_bshd, v_bshd, layout.indices, layout.counts, store)
     valid_k = _valid_k(device, prefix_tokens, query_block_size, _counts_key(layout))
     status = torch.zeros(1, dtype=torch.int32, device=device)
 
     if native_prefix:
         side.wait_stream(current)
         with torch.cuda.stream(side):
-            prefix_out = native.prefix_attention(shape, store, valid_k, status)
+            with _Stage("prefix_attention"):
+                prefix_out = native.prefix_attention(shape, store, valid_k, status)
             for t in store.buffers.values():
                 if t is not None:
                     t.record_stream(side)
             valid_k.record_stream(side)
             status.record_stream(side)
 
-    prob = native.draft_probability(shape, store, float(maxpool_weight))
+    with _Stage("draft"):
+        prob = native.draft_probability(shape, store, float(maxpool_weight))
     n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=float(sparsity_ratio),
                                nvfp4_ratio=float(retained_nvfp4_ratio),
                                int8_ratio=float(retained_int8_ratio),
                                fp16_ratio=float(retained_fp16_ratio))
     phase_index = -1 if prefix_phase is None else PHASE_ORDER.index(prefix_phase)
-    lists = native.route(shape, prob, n16, n8, n4, phase_index)
-    packed = native.attention(shape, store, lists, valid_k, status)
+    with _Stage("route"):
+        lists = native.route(shape, prob, n16, n8, n4, phase_index)
+    with _Stage("attention"):
+        packed = native.attention(shape, store, lists, valid_k, status)
 
     current.wait_stream(side)
     if prefix_out is not None:
         prefix_out.record_stream(current)
-    out = native.assemble(shape, prefix_out, packed, layout.inverse, lists.row_counts, q_bshd.dtype)
+    with _Stage("assemble"):
+        out = native.assemble(shape, prefix_out, packed, layout.inverse, lists.row_counts,
+                              q_bshd.dtype)
     _LAST_STATUS[device] = status
     if return_parts:
         return out, dict(shape=shape, store=store, prob=prob, lists=lists, packed=packed,

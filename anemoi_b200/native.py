@@ -71,7 +71,7 @@ def library() -> C.CDLL:
     signatures = {
         "anemoi_sm100_arch": (C.c_int, []),
         "anemoi_sm100_operand_bytes": (I64, [SP, C.c_int]),
-        "anemoi_sm100_prepare": (C.c_int, [SP, P, P, P, P, P, OP, P]),
+        "anemoi_sm100_prepare": (C.c_int, [SP, P, P, P, C.POINTER(I64), P, P, OP, P]),
         "anemoi_sm100_draft_probability": (C.c_int, [SP, P, P, P, P, F, P, P]),
         "anemoi_sm100_route_scratch_bytes": (I64, [SP]),
         "anemoi_sm100_route_list_capacity": (I64, [SP, I64, I64, I64, C.c_int]),
@@ -167,10 +167,11 @@ def allocate_operands(shape: Shape, device) -> OperandStore:
 
 
 def prepare(shape: Shape, q, k, v, indices, counts, store: OperandStore) -> None:
-    """Fill the operand store from raw ``[1, S, H, D]`` Q/K/V (see anemoi_sm100_prepare)."""
-    _check(library().anemoi_sm100_prepare(C.byref(shape), _ptr(q), _ptr(k), _ptr(v), _ptr(indices),
-                                          _ptr(counts), C.byref(store.struct), _stream(q.device)),
-           "anemoi_sm100_prepare")
+    """Fill the operand store from raw ``[1, S, H, D]`` Q/K/V views (see anemoi_sm100_prepare)."""
+    strides = (C.c_int64 * 6)(q.stride(1), q.stride(2), k.stride(1), k.stride(2), v.stride(1), v.stride(2))
+    _check(library().anemoi_sm100_prepare(C.byref(shape), _ptr(q), _ptr(k), _ptr(v), strides,
+                                          _ptr(indices), _ptr(counts), C.byref(store.struct),
+                                          _stream(q.device)), "anemoi_sm100_prepare")
 
 
 def draft_probability(shape: Shape, store: OperandStore, maxpool_weight: float) -> torch.Tensor:
@@ -264,6 +265,8 @@ def pack_qkv_destination_major(q, k, v, world: int) -> torch.Tensor:
     if q.element_size() != 2 or any(t.stride(-1) != 1 for t in (q, k, v)):
         raise ValueError("pack_qkv needs 16-bit tensors with a contiguous head dimension")
     out = torch.empty((world, rows, heads // world, 3 * d), dtype=q.dtype, device=q.device)
+    if out.numel() == 0:
+        return out
     strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
     _check(library().anemoi_sm100_pack_qkv(_ptr(q), _ptr(k), _ptr(v), _ptr(out), rows, heads, d,
                                            world, strides, _stream(q.device)),
@@ -277,6 +280,8 @@ def merge_heads(x: torch.Tensor) -> torch.Tensor:
     if not x.is_contiguous() or x.element_size() != 2:
         raise ValueError("merge_heads needs a contiguous 16-bit tensor")
     out = torch.empty((rows, world * hl, d), dtype=x.dtype, device=x.device)
+    if out.numel() == 0:
+        return out
     _check(library().anemoi_sm100_merge_heads(_ptr(x), _ptr(out), rows, world, hl, d,
                                               _stream(x.device)), "anemoi_sm100_merge_heads")
     return out

@@ -1,0 +1,125 @@
+"""Ulysses sequence<->head exchange around ``anemoi_attention`` for 1/2/4/8 B200s of one node.
+
+Every rank holds a contiguous slice of the packed sequence with all heads.  One
+all-to-all carries q, k and v together to head-sharded form (each rank: the whole
+sequence, ``heads / world`` heads), attention runs on the local heads, and a second
+all-to-all brings the output back to sequence-sharded form.  Heads are independent
+in every stage of the attention path, so the sharded result is bit-identical to the
+single-GPU result.
+
+Follows the reference's custom Ulysses path
+(anemoi/models/minimax_h3/solengine/models/minimax_h3/optimized/ulysses_custom.py:36-165,
+relayout.py:83-162): packed destination-major send buffer, explicit split sizes for
+uneven shards (``tensor_split`` row counts, gathered once per group and cached),
+plain ``all_to_all_single`` without the functional-collective wrapper.  The relayouts
+are CUDA copy kernels of this library instead of Triton kernels, and the head-sharded
+receive buffer is consumed in place by the preparation kernel (strided Q/K/V views),
+so no unpack pass exists.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import native
+from .api import NVFP4Calibration, QuantConfig, SparseConfig, VisualLayout, anemoi_attention
+
+_ROW_COUNTS: dict = {}
+
+
+def shard_rows(total_rows: int, world: int) -> list[int]:
+    """Row counts of ``torch.tensor_split(total_rows, world)``: the first ``total % world``
+    ranks hold one row more."""
+    base, extra = divmod(total_rows, world)
+    return [base + (1 if r < extra else 0) for r in range(world)]
+
+
+def row_counts(rows_local: int, group=None) -> list[int]:
+    """Every rank's row count; one ``all_reduce`` per group, then cached.
+
+    The cache key is the group (identical on every rank) and a changed local length
+    raises instead of desynchronising the collective count across ranks."""
+    key = id(group)
+    cached = _ROW_COUNTS.get(key)
+    if cached is not None:
+        counts, seen = cached
+        if seen != rows_local:
+            raise RuntimeError(
+                f"row count cached for rows_local={seen} but called with {rows_local}; "
+                "call reset_row_counts() on every rank when the sequence length changes")
+        return counts
+    world = dist.get_world_size(group)
+    device = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    buf = torch.zeros(world, dtype=torch.long, device=device)
+    buf[dist.get_rank(group)] = rows_local
+    dist.all_reduce(buf, group=group)
+    counts = [int(c) for c in buf.tolist()]
+    _ROW_COUNTS[key] = (counts, rows_local)
+    return counts
+
+
+def reset_row_counts() -> None:
+    _ROW_COUNTS.clear()
+
+
+def exchange_to_heads(q, k, v, counts, group=None, pack=native.pack_qkv_destination_major):
+    """``(rows_local, H, D)`` x3 -> ``(S, H/world, 3*D)`` on every rank (one collective)."""
+    world = len(counts)
+    rows, heads, d = q.shape
+    h_local = heads // world
+    send = pack(q, k, v, world)                              # (world, rows, h_local, 3D)
+    inner = h_local * 3 * d
+    recv = torch.empty((sum(counts), h_local, 3 * d), dtype=q.dtype, device=q.device)
+    dist.all_to_all_single(recv.view(-1), send.view(-1),
+                           output_split_sizes=[c * inner for c in counts],
+                           input_split_sizes=[rows * inner] * world, group=group)
+    return recv
+
+
+def exchange_to_sequence(out_heads, counts, rank: int, group=None, merge=native.merge_heads):
+    """``(S, H/world, D)`` -> ``(rows_local, H, D)`` (one collective + one merge copy)."""
+    world = len(counts)
+    s, h_local, d = out_heads.shape
+    rows = counts[rank]
+    inner = h_local * d
+    recv = torch.empty((world, rows, h_local, d), dtype=out_heads.dtype, device=out_heads.device)
+    dist.all_to_all_single(recv.view(-1), out_heads.reshape(-1),
+                           output_split_sizes=[rows * inner] * world,
+                           input_split_sizes=[c * inner for c in counts], group=group)
+    return merge(recv)
+
+
+def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_destination_major,
+                      merge=native.merge_heads):
+    """Head-shard, run ``attention_fn(q, k, v)`` on ``[1, S, H/world, D]`` views, shard back.
+
+    ``q, k, v``: ``[1, rows_local, H, D]`` (this rank's rows, every head).  Returns
+    ``[1, rows_local, H, D]``."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return attention_fn(q, k, v)
+    rank = dist.get_rank(group)
+    heads, d = q.size(2), q.size(3)
+    if heads % world:
+        raise ValueError(f"heads ({heads}) must divide the Ulysses degree ({world})")
+    counts = row_counts(q.size(1), group)
+    packed = exchange_to_heads(q[0], k[0], v[0], counts, group, pack)    # (S, h, 3D)
+    qh, kh, vh = (packed[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
+    out = attention_fn(qh, kh, vh)                                       # [1, S, h, D]
+    return exchange_to_sequence(out[0].contiguous(), counts, rank, group, merge).unsqueeze(0)
+
+
+def ulysses_anemoi_attention(q, k, v, *, layout: VisualLayout, layer: int,
+                             sparse_config: SparseConfig | None = None,
+                             quant_config: QuantConfig | None = None,
+                             calibration: NVFP4Calibration | None = None, group=None):
+    """``anemoi_attention`` with the heads sharded over the ranks of ``group``."""
+    def local(qh, kh, vh):
+        return anemoi_attention(qh, kh, vh, layout=layout, layer=layer, sparse_config=sparse_config,
+                                quant_config=quant_config, calibration=calibration)
+    return ulysses_attention(q, k, v, local, group)
+
+
+__all__ = ["shard_rows", "row_counts", "reset_row_counts", "exchange_to_heads",
+           "exchange_to_sequence", "ulysses_attention", "ulysses_anemoi_attention"]

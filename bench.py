@@ -1,0 +1,412 @@
+"""Benchmark of the sparse mixed-precision attention layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[2], the configuration the metric is quoted on):
+512-token prefix + 21x48x84 video tokens (S = 85,184), 56 heads, D = 128, bf16,
+Q128 query blocks, 80 % of block pairs dropped, retained pairs split NVFP4 / INT8 /
+FP16 = 40 / 40 / 20, NVFP4 global scales amax/(6*448).  Inputs are seeded synthetic
+tensors with the smooth-field statistics of the reference's captured Q/K/V.
+
+One "step" is one whole ``anemoi_attention`` layer call.  ``value`` is the
+dense-equivalent throughput 4*S^2*D*H / time with inputs resident in HBM; ``e2e``
+is the same metric through the public API with pinned-host inputs copied to the
+device and the result copied back inside the timed region.  With N > 1 the heads
+are sharded over N GPUs by a Ulysses sequence<->head all-to-all (strong scaling).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "sparse-attn layer ms & dense-equiv TFLOPS @84,672 tok, 1/2/4/8 B200"
+WORKLOAD = dict(prefix=512, video=(21, 48, 84), heads=56, dim=128, query_block=128, drop=0.8,
+                ratios=(0.4, 0.4, 0.2), maxpool=0.0, outliers=(17, 93))
+# Small case for profiler captures only (never a bench line): same cells and block shapes,
+# 8 heads of the 832x480 geometry - about 0.5 GB on the device, inputs still larger than L2.
+PROFILE_WORKLOAD = dict(WORKLOAD, video=(21, 30, 52), heads=8)
+
+
+def dense_equivalent_flops(s: int, d: int, h: int) -> float:
+    return 4.0 * s * s * d * h
+
+
+def executed_flops(w, kept_pairs: int, blocks: int) -> float:
+    """FLOPs the attention kernels execute per layer: retained pairs + prefix columns + prefix rows."""
+    qb, d, h = w["query_block"], w["dim"], w["heads"]
+    p = math.ceil(w["prefix"] / 64)
+    kp = 64 * p + blocks * qb
+    rows_prefix = math.ceil(w["prefix"] / qb) * qb
+    return 4.0 * d * h * (kept_pairs * qb * qb + blocks * qb * 64 * p + rows_prefix * kp)
+
+
+def synth_qkv(w, heads: int, device, seed: int, rows: slice | None = None, dtype=torch.bfloat16):
+    """Seeded smooth-field Q/K/V ``[1, S, heads, D]`` (see module docstring)."""
+    f, hh, ww = w["video"]
+    d, prefix = w["dim"], w["prefix"]
+    gen = torch.Generator(device=device).manual_seed(seed)
+    radius = 6
+    taps = torch.exp(-0.5 * (torch.arange(-radius, radius + 1, dtype=torch.float32, device=device) / 2.0) ** 2)
+    taps = taps / taps.sum()
+
+    def field():
+        out = torch.empty(prefix + f * hh * ww, heads, d, dtype=dtype, device=device)
+        out[:prefix] = torch.randn(prefix, heads, d, generator=gen, device=device).to(dtype)
+        for h in range(heads):
+            x = torch.randn(f, d, hh, ww, generator=gen, device=device)
+            x = torch.nn.functional.pad(x, (0, 0, radius, radius), mode="reflect")
+            x = torch.nn.functional.conv2d(x, taps.view(1, 1, -1, 1).expand(d, 1, -1, 1), groups=d)
+            x = torch.nn.functional.pad(x, (radius, radius, 0, 0), mode="reflect")
+            x = torch.nn.functional.conv2d(x, taps.view(1, 1, 1, -1).expand(d, 1, 1, -1), groups=d)
+            x = x + 0.5 * torch.randn(x.shape, generator=gen, device=device)
+            for ch in w["outliers"]:
+                x[:, ch] *= 8.0
+            out[prefix:, h] = x.permute(0, 2, 3, 1).reshape(f * hh * ww, d).to(dtype)
+        return out.unsqueeze(0)
+
+    q, k = field(), field()
+    v = torch.randn(1, prefix + f * hh * ww, heads, d, generator=gen, device=device).to(dtype)
+    if rows is not None:
+        q, k, v = (t[:, rows].contiguous() for t in (q, k, v))
+    return q, k, v
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+            self.thread.join(timeout=2)
+        return False
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement of the reference's algorithm on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_sample(w, query_blocks: int, seed: int = 1) -> dict:
+    """Time one head of the workload on the CPU with ``query_blocks`` query blocks of attention
+    and extrapolate to the whole layer (heads and query blocks are independent)."""
+    import numpy as np
+
+    from anemoi_b200.partition import make_ragged_2d_partition
+    from oracle import attention as A, prep as P, route as R
+    from oracle.pipeline import resolve
+
+    f, hh, ww = w["video"]
+    q, k, v = synth_qkv(w, 1, torch.device("cpu"), seed)
+    amax = [float(t.float().abs().max()) / (6 * 448) for t in (q, k, v)]
+    t0 = time.perf_counter()
+    part = make_ragged_2d_partition(hh, ww, w["query_block"], include_adjacency=False)
+    t_partition = time.perf_counter() - t0
+    geo = P.make_geometry(part.blocks, f, hh, ww, w["query_block"], w["prefix"])
+    r4, r8, r16 = w["ratios"]
+    _, active, prefix_phase = resolve(r4, r8, r16, w["prefix"], "int8")
+    t0 = time.perf_counter()
+    ops = P.prepare_head(q[0, :, 0], k[0, :, 0], v[0, :, 0], geo, has_nvfp4="nvfp4" in active,
+                         has_int8="int8" in active, has_prefix_query_int8=True,
+                         has_maxpool=w["maxpool"] != 0.0, global_scales=tuple(amax))
+    t_prep = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    prob = R.draft_probability(ops.q_pool, ops.k_pool, ops.q_max, ops.k_max, w["maxpool"])
+    rr = geo.video_blocks
+    n16, n8, n4 = R.budgets(rr * rr, w["drop"], r4, r8, r16)
+    ids, low, mid, high = R.route(prob, n16, n8, n4)
+    lists = R.stage_lists(ids, low, mid, high, query_block=geo.query_block,
+                          prefix_stages=geo.prefix_stages, prefix_phase=prefix_phase)
+    t_route = time.perf_counter() - t0
+    qb = geo.query_block
+    pick = np.linspace(0, rr - 1, query_blocks).astype(int)
+    t0 = time.perf_counter()
+    stages_done = 0
+    for i in pick:
+        A.attention_rows(ops, geo, slice(i * qb, (i + 1) * qb), lists[i], head_dim=w["dim"],
+                         q_scale_index=int(i), global_scales=tuple(amax))
+        stages_done += sum(len(x) for x in lists[i])
+    t_attn = time.perf_counter() - t0
+    stages_all = sum(sum(len(x) for x in row) for row in lists)
+    prefix_stage_work = math.ceil(w["prefix"] / qb) * geo.stages
+    t_head = t_prep + t_route + t_attn * (stages_all + prefix_stage_work) / max(stages_done, 1)
+    layer_s = t_head * w["heads"]
+    s = w["prefix"] + f * hh * ww
+    return {
+        "layer_seconds": layer_s,
+        "tflops": dense_equivalent_flops(s, w["dim"], w["heads"]) / layer_s / 1e12,
+        "sample": (f"one head of the workload: gather/quantise {t_prep:.2f}s + draft/route {t_route:.2f}s "
+                   f"+ {query_blocks} of {rr} query blocks of attention {t_attn:.2f}s, scaled by stages "
+                   f"and x{w['heads']} heads (partition search {t_partition:.2f}s, once per geometry, not counted)"),
+        "cores": os.cpu_count(),
+        "sample_seconds": t_prep + t_route + t_attn,
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    last = None
+    for i in range(args.warmup + args.steps):
+        last = cpu_sample(WORKLOAD, query_blocks=2, seed=1 + i)
+        if i >= args.warmup:
+            times.append(last["layer_seconds"])
+    mean_s = sum(times) / len(times)
+    w = WORKLOAD
+    s = w["prefix"] + math.prod(w["video"])
+    value = dense_equivalent_flops(s, w["dim"], w["heads"]) / mean_s / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s dense-equivalent",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean_s * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s dense-equivalent", "cores": last["cores"],
+                         "kind": "port", "sample": last["sample"]},
+        "e2e": {"value": value, "unit": "TFLOP/s dense-equivalent", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int) -> dict:
+    w = WORKLOAD
+    return {"workload": "BASELINE configs[2]: prefix 512 + video 21x48x84 (S=85184), H=56, D=128, bf16, "
+                        "Q128, 80% block drop, NVFP4/INT8/FP16 = 40/40/20, prefix K/V and prefix queries INT8",
+            "parallelism": f"ulysses{n_gpus}" if n_gpus > 1 else "single",
+            "heads_per_gpu": w["heads"] // n_gpus,
+            "l2": "inputs (3.66 GB of Q/K/V) exceed the 126 MB L2; no explicit flush"}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    from anemoi_b200 import NVFP4Calibration, QuantConfig, SparseConfig, VisualLayout, anemoi_attention
+    from anemoi_b200 import executor
+    from anemoi_b200.build import build
+    from anemoi_b200.routing import route_counts
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if rank == 0:
+        build()
+    if world > 1:
+        dist.barrier()
+
+    w = WORKLOAD
+    s_total = w["prefix"] + math.prod(w["video"])
+    layout = VisualLayout(w["video"], w["prefix"])
+    sparse = SparseConfig(w["query_block"], w["drop"], (), w["maxpool"])
+    quant = QuantConfig(*w["ratios"], "int8", "int8")
+
+    if world == 1:
+        q, k, v = synth_qkv(w, w["heads"], device, seed=0)
+    else:
+        from anemoi_b200 import ulysses
+
+        rows = ulysses.shard_rows(s_total, world)
+        lo = sum(rows[:rank])
+        # every rank draws the same seeded tensors head by head and keeps its sequence shard
+        q, k, v = synth_qkv(w, w["heads"], device, seed=0, rows=slice(lo, lo + rows[rank]))
+    amax = torch.stack([t.float().abs().max() for t in (q, k, v)])
+    if world > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+    calib = NVFP4Calibration(*[float(a) / (6 * 448) for a in amax.tolist()])
+
+    def layer(qq, kk, vv):
+        if world == 1:
+            return anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
+                                    quant_config=quant, calibration=calib)
+        return ulysses.ulysses_anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
+                                                quant_config=quant, calibration=calib)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        out = layer(q, k, v)
+    barrier()
+    if executor.last_status(device) != 0:
+        raise SystemExit("attention kernel reported an aborted wait")
+
+    # ---- timed: inputs resident in HBM ----
+    executor.collect_stage_events(True)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            out = layer(q, k, v)
+        end.record()
+        barrier()
+    ms = start.elapsed_time(end) / args.steps
+    stages = {kk: vv / args.steps for kk, vv in executor.stage_times_ms().items()}
+    executor.collect_stage_events(False)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    # ---- timed: end to end from pinned host memory ----
+    hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
+    hout = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+
+    def e2e_step():
+        dq, dk, dv = (x.to(device, non_blocking=True) for x in (hq, hk, hv))
+        hout.copy_(layer(dq, dk, dv), non_blocking=True)
+
+    for _ in range(min(args.warmup, 2)):
+        e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 5))
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    end.record()
+    barrier()
+    te = torch.tensor([start.elapsed_time(end) / e2e_steps], device=device)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item())
+
+    if rank == 0:
+        from anemoi_b200.layout import materialize_ragged_2d_layout
+
+        blocks = materialize_ragged_2d_layout("cpu", frames=w["video"][0], height=w["video"][1],
+                                              width=w["video"][2], logical_block=w["query_block"]).video_blocks
+        n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=w["drop"], nvfp4_ratio=w["ratios"][0],
+                                   int8_ratio=w["ratios"][1], fp16_ratio=w["ratios"][2])
+        flops = dense_equivalent_flops(s_total, w["dim"], w["heads"])
+        peaks, peak_kind = measured_peaks()
+        bf16 = float(peaks["bf16_tflops"])
+        qb, d, p = w["query_block"], w["dim"], math.ceil(w["prefix"] / 64)
+        per_head = 4.0 * d
+        f4 = per_head * n4 * qb * qb
+        f8 = per_head * (n8 * qb * qb + blocks * qb * 64 * p)
+        f16 = per_head * n16 * qb * qb
+        heads_local = w["heads"] // world
+        video_flops = heads_local * (f4 + f8 + f16)
+        # per-dtype tensor peaks relative to the measured bf16 GEMM: 8-bit kinds 2x, NVFP4 4x (nominal ratios)
+        mixed_peak = (f4 + f8 + f16) / (f4 / (4 * bf16) + f8 / (2 * bf16) + f16 / bf16)
+        attn_ms = stages.get("attention", float("nan"))
+        achieved = video_flops / (attn_ms * 1e-3) / 1e12 if attn_ms == attn_ms else None
+        line = {
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4+int8/e4m3+fp16 (fp32 accumulate)", "data": "synthetic",
+            "config": workload_config(world),
+            "clocks": clocks.summary(),
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
+                    "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in (q, k, v))),
+                    "d2h_bytes_per_step": int(out.numel() * out.element_size())},
+            "gpu_launches": 10 + (2 if world > 1 else 0),
+            "stage_ms": stages,
+            "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
+                         "achieved": achieved, "peak": mixed_peak, "unit": "TFLOP/s",
+                         "frac": (achieved / mixed_peak) if achieved else None, "traffic": None,
+                         "peak_source": f"{peak_kind} bf16 GEMM {bf16} TFLOP/s x (1, 2, 4) for fp16, 8-bit, NVFP4 "
+                                        "cells, weighted by executed FLOPs"},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_sample(w, query_blocks=3)
+            line["cpu_baseline"] = {"value": cpu["tflops"], "unit": "TFLOP/s dense-equivalent",
+                                    "cores": cpu["cores"], "kind": "port", "sample": cpu["sample"]}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run the small profiling case instead of the benchmark workload")
+    args = ap.parse_args()
+    if args.profile_case:
+        WORKLOAD.update(PROFILE_WORKLOAD)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -84,15 +84,19 @@ int anemoi_sm100_arch(void);
  * inactive; negative on a bad shape. */
 int64_t anemoi_sm100_operand_bytes(const anemoi_sm100_shape* shape, int which);
 
-/* Gather + narrow + pool + quantise in one pass over raw Q/K/V ([1,S,H,D]
- * contiguous, bf16 or fp16).  `indices` int32 [R*QB] (slot -> video token),
- * `counts` int32 [R] (real tokens per block).
+/* Gather + narrow + pool + quantise in one pass over raw Q/K/V (logical
+ * [1,S,H,D], bf16 or fp16, D contiguous).  `strides` = token and head stride in
+ * elements of q, k, v (6 values, multiples of 8), or null for contiguous
+ * [1,S,H,D]; strided views let the head-sharded buffer of a Ulysses exchange be
+ * consumed in place (the reference accepts its BSHD-strided view the same way,
+ * csrc/common/raw_bhsd_layout.h:15-28).  `indices` int32 [R*QB] (slot -> video
+ * token), `counts` int32 [R] (real tokens per block).
  * Replaces prepare_h3_sm120_operands (sm120/bindings.cpp, kernels in
  * sm120/q128_microscaling_preparation.cu:245-803) and, for the pure FP16 cell,
  * pack_h3_k64_qkv_fp16 + the torch pools (mpa/executor.py:83-108). */
 int anemoi_sm100_prepare(const anemoi_sm100_shape* shape, const void* q, const void* k,
-                         const void* v, const int32_t* indices, const int32_t* counts,
-                         const anemoi_sm100_operands* out, void* stream);
+                         const void* v, const int64_t* strides, const int32_t* indices,
+                         const int32_t* counts, const anemoi_sm100_operands* out, void* stream);
 
 /* Pooled-QK row softmax -> fp16 probability [H][R][R]; with 0 < w < 1 the mean
  * and max maps are blended, w == 1 uses the max pools only.

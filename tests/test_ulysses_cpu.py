@@ -1,0 +1,79 @@
+"""Host logic of the Ulysses exchange on two CPU ranks (gloo): uneven shards, row-count cache,
+and equality with the unsharded computation.  The CUDA relayout kernels are replaced by the
+torch permutes they are defined to equal (relayout.py:110-119,143-149 of the reference)."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from anemoi_b200 import ulysses
+
+
+def torch_pack(q, k, v, world):
+    rows, heads, d = q.shape
+    hl = heads // world
+    out = torch.empty((world, rows, hl, 3 * d), dtype=q.dtype)
+    for i, t in enumerate((q, k, v)):
+        out[..., i * d : (i + 1) * d] = t.reshape(rows, world, hl, d).permute(1, 0, 2, 3)
+    return out
+
+
+def torch_merge(x):
+    world, rows, hl, d = x.shape
+    return x.permute(1, 0, 2, 3).contiguous().reshape(rows, world * hl, d)
+
+
+def toy_attention(q, k, v):
+    # per-head dense attention: any head-independent function exercises the exchange
+    qh, kh, vh = (t[0].permute(1, 0, 2).float() for t in (q, k, v))
+    p = torch.softmax(qh @ kh.transpose(1, 2) / q.size(-1) ** 0.5, dim=-1)
+    return (p @ vh).permute(1, 0, 2).unsqueeze(0).to(q.dtype)
+
+
+def _worker(rank, world, port, total_rows, heads, d, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(5)
+        full = [torch.randn(1, total_rows, heads, d, generator=gen).to(torch.bfloat16) for _ in range(3)]
+        rows = ulysses.shard_rows(total_rows, world)
+        lo = sum(rows[:rank])
+        mine = [t[:, lo : lo + rows[rank]].contiguous() for t in full]
+        got = ulysses.ulysses_attention(*mine, toy_attention, pack=torch_pack, merge=torch_merge)
+        want = toy_attention(*full)[:, lo : lo + rows[rank]]
+        ok = torch.equal(got, want)
+        counts = ulysses.row_counts(rows[rank])
+        # a changed local length without a reset must fail loudly, not desynchronise
+        raised = False
+        try:
+            ulysses.row_counts(rows[rank] + 1)
+        except RuntimeError:
+            raised = True
+        results[rank] = (ok, counts == rows, raised)
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("total_rows", [37, 40])
+def test_two_rank_exchange_matches_unsharded(total_rows):
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), total_rows, 4, 16, results), nprocs=world, join=True)
+    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
+
+
+def test_shard_rows_matches_tensor_split():
+    for total, world in ((38247, 4), (85184, 8), (7, 8), (33272, 8)):
+        want = [t.numel() for t in torch.tensor_split(torch.arange(total), world)]
+        assert ulysses.shard_rows(total, world) == want
