@@ -30,6 +30,7 @@
 //   FP16 : P -> f16
 // Accumulation is fp32 in TMEM (the reference accumulates a stage in fp16 for the
 // INT8 and FP16 cells).
+#include <cstdlib>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
@@ -49,8 +50,9 @@ constexpr int kColSfaQ = 192;  // 2 k-steps x 4 columns
 constexpr int kColSfbK = 200;  // 2 k-steps x 4 columns
 constexpr int kColSfaP = 208;
 constexpr int kColSfbV = 212;
-constexpr int kMaxSlots = 4;
+constexpr int kMaxSlots = 8;
 constexpr float kFp8Offset = 8.807f;
+constexpr bool kPolyShare = false;  // true: every 4th probability uses ex2_poly
 
 enum Cell : int { kNv = 0, kI8 = 1, kF16 = 2 };
 
@@ -68,10 +70,10 @@ struct AttnParams {
   int stages;        // 64-key stages per head
   int q_tiles_int8;  // records per head in q_int8 (R + prefix query tiles)
   int out_rows;      // rows per head in `out`
-  int nslot;
-  int slot_bytes;
+  int ring_bytes;    // key/value ring; re-partitioned into equal slots at every phase
   int q_region;      // bytes
   int p_region;      // bytes
+  int debug;         // TEMP experiment flags
 };
 
 struct Barriers {
@@ -195,6 +197,18 @@ __device__ __forceinline__ void write_p(uint8_t* p_smem, int row, const float (&
   }
 }
 
+// 2^x on the FMA/ALU pipes (Cody-Waite split + degree-3 polynomial, relative error ~1e-4),
+// used for a share of the probabilities so the MUFU unit is not the only exp engine.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float xr = x + 12582912.0f;             // 1.5 * 2^23: integer part lands in the low mantissa bits
+  const float f = x - (xr - 12582912.0f);      // fractional part in [-0.5, 0.5]
+  float p = fmaf(f, 0.05550410866f, 0.2402265069f);
+  p = fmaf(p, f, 0.6931471806f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
 // One stage of one phase for the thread's row.  Returns false on an aborted wait.
 template <int CELL, int D>
 __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
@@ -212,34 +226,58 @@ __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, 
   }
   float s[64];
   {
-    uint32_t r[32];
-    tmem_ld32(tmem_row + kColS, r);
+    uint32_t r0[32], r1[32];
+    tmem_ld32(tmem_row + kColS, r0);
+    tmem_ld32(tmem_row + kColS + 32, r1);
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      s[j] = CELL == kI8 ? (float)(int)r[j] : __uint_as_float(r[j]);
-    tmem_ld32(tmem_row + kColS + 32, r);
-    tmem_wait_ld();
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      s[32 + j] = CELL == kI8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+    for (int j = 0; j < 32; ++j) {
+      if (CELL == kI8) {
+        // exact s32 -> f32 for |x| < 2^22 without the conversion unit
+        s[j] = __int_as_float((int)r0[j] + 0x4B400000) - 12582912.0f;
+        s[32 + j] = __int_as_float((int)r1[j] + 0x4B400000) - 12582912.0f;
+      } else {
+        s[j] = __uint_as_float(r0[j]);
+        s[32 + j] = __uint_as_float(r1[j]);
+      }
+    }
   }
   tc_fence_before_sync();
   mbar_arrive(&b->s_free);
 
-  float mx = -INFINITY;
+  if (valid < 64) {
 #pragma unroll
-  for (int j = 0; j < 64; ++j) mx = fmaxf(mx, j < valid ? s[j] : -INFINITY);
+    for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+  }
+  float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+#pragma unroll
+  for (int j = 4; j < 64; j += 2) {
+    mx0 = fmaxf(mx0, s[j]);
+    mx1 = fmaxf(mx1, s[j + 1]);
+  }
+  const float mx = fmaxf(mx0, mx1);
   const float m_new = fmaxf(st.m, mx * score_scale);
   const float alpha = ex2(st.m - m_new);
   const float bias = CELL == kI8 ? kFp8Offset - m_new : -m_new;
-  float sum = 0.0f;
+  float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+  if (!(p.debug & 4))
 #pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    const float e = j < valid ? ex2(fmaf(s[j], score_scale, bias)) : 0.0f;
-    s[j] = e;
-    sum += e;
+  for (int j = 0; j < 64; j += 4) {
+    const float e0 = ex2(fmaf(s[j], score_scale, bias));
+    const float e1 = ex2(fmaf(s[j + 1], score_scale, bias));
+    const float e2 = ex2(fmaf(s[j + 2], score_scale, bias));
+    const float e3 = kPolyShare ? ex2_poly(fmaf(s[j + 3], score_scale, bias))
+                                : ex2(fmaf(s[j + 3], score_scale, bias));
+    s[j] = e0;
+    s[j + 1] = e1;
+    s[j + 2] = e2;
+    s[j + 3] = e3;
+    sum0 += e0;
+    sum1 += e1;
+    sum2 += e2;
+    sum3 += e3;
   }
+  float sum = (sum0 + sum1) + (sum2 + sum3);
   if (CELL == kI8) sum *= 0.0022326917f;  // 2^-8.807
   st.d = st.d * alpha + sum;
   st.m = m_new;
@@ -249,9 +287,9 @@ __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, 
     if (!wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
     tc_fence_after_sync();
     const bool need = phase_first || __any_sync(0xffffffffu, alpha != 1.0f);
-    if (need) rescale_o<D>(tmem_row, alpha, phase_first ? colf : nullptr);
+    if (need && !(p.debug & 1)) rescale_o<D>(tmem_row, alpha, phase_first ? colf : nullptr);
   }
-  write_p<CELL>(p_smem, row, s);
+  if (!(p.debug & 2)) write_p<CELL>(p_smem, row, s);
   fence_proxy_async_smem();
   tc_fence_before_sync();
   mbar_arrive(&b->p_full);
@@ -353,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
   uint8_t* q_smem = smem;
   uint8_t* p_smem = smem + p.q_region;
   uint8_t* slots = p_smem + p.p_region;
-  float* colf = reinterpret_cast<float*>(slots + (size_t)p.nslot * p.slot_bytes);
+  float* colf = reinterpret_cast<float*>(slots + (size_t)p.ring_bytes);
   Barriers* b = reinterpret_cast<Barriers*>(colf + D);
 
   if (threadIdx.x == 0) {
@@ -389,7 +427,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
   if (warp == 4) {
     // =============================== loader ===============================
     if (lane == 0) {
-      int g = 0, phase_ord = 0;
+      int phase_ord = 0;
+      uint32_t filled = 0, fillpar = 0;  // per slot: ever filled / parity of the fill count
       bool ok = true;
       for (int cell = 0; cell < 3 && ok; ++cell) {
         if (cnt[cell] == 0) continue;
@@ -416,14 +455,24 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
                            : static_cast<const uint8_t*>(p.o.kv_fp16)) +
             (int64_t)head * p.stages * kvbytes;
         const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
-        for (int i = 0; i < cnt[cell] && ok; ++i, ++g) {
-          const int slot = g % p.nslot, use = g / p.nslot;
-          if (use > 0) ok = wait(b, &b->kv_free[slot], (use - 1) & 1, p.status, 2);
+        // The ring is cut into equal slots of this phase's record size; slots of the
+        // previous phase must all be released before the new geometry is written.
+        const int slot_bytes = (kvbytes + 127) & ~127;
+        const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
+        for (int sl = 0; sl < kMaxSlots && ok; ++sl)
+          if ((filled >> sl) & 1u)
+            ok = wait(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
+        for (int i = 0; i < cnt[cell] && ok; ++i) {
+          const int slot = i % nslot;
+          if ((filled >> slot) & 1u)
+            ok = wait(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
           if (!ok) break;
           const int stage = list ? list[first + i] : i;
           mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes);
-          bulk_g2s(slots + (size_t)slot * p.slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
+          bulk_g2s(slots + (size_t)slot * slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
                    &b->kv_full[slot]);
+          filled |= 1u << slot;
+          fillpar ^= 1u << slot;
         }
         ++phase_ord;
       }
@@ -432,6 +481,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     // =============================== MMA issue ===============================
     if (lane == 0) {
       int g = 0, phase_ord = 0;
+      uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
       bool ok = true;
       const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
       for (int cell = 0; cell < 3 && ok; ++cell) {
@@ -446,27 +496,30 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
             tmem_cp_32x128b_warpx4(tmem + kColSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128));
         }
         const int n = cnt[cell];
+        const int slot_bytes = (CellInfo<D>::kv_bytes(cell) + 127) & ~127;
+        const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
         // software pipeline: QK of stage i+1 is issued before PV of stage i
         for (int i = 0; i <= n && ok; ++i) {
           if (i < n) {
             const int gi = g + i;
-            const int slot = gi % p.nslot, use = gi / p.nslot;
-            ok = wait(b, &b->kv_full[slot], use & 1, p.status, 4);
+            const int slot = i % nslot;
+            ok = wait(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
+            usepar ^= 1u << slot;
             if (ok && gi > 0) ok = wait(b, &b->s_free, (gi - 1) & 1, p.status, 5);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * p.slot_bytes);
+            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * slot_bytes);
             issue_qk<D>(cell, tmem, q_addr, slot_addr, slot_addr);
             mma_commit(&b->s_full);
             if (i == n - 1) mma_commit(&b->q_free);
           }
           if (i > 0) {
             const int gj = g + i - 1;
-            const int slot = gj % p.nslot;
+            const int slot = (i - 1) % nslot;
             ok = wait(b, &b->p_full, gj & 1, p.status, 6);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * p.slot_bytes);
+            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * slot_bytes);
             issue_pv<D>(cell, tmem, p_addr, slot_addr, gj > 0);
             mma_commit(&b->o_done);
             mma_commit(&b->kv_free[slot]);
@@ -510,15 +563,28 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           cell == kI8 ? p.o.q_int8_scale[q_index_i8] : 1.0f;
       const float base_scale =
           cell == kNv ? sigma * p.s.q_global_scale * p.s.k_global_scale : sigma;
+      // Per-stage metadata (stage id -> real keys, key scale) is fetched 32 stages at a
+      // time, one stage per lane, and handed out with shuffles: no dependent global
+      // loads sit on the per-stage critical path.
+      int meta_valid = 64;
+      float meta_scale = 1.0f;
+      const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
       for (int i = 0; i < cnt[cell] && ok; ++i, ++g) {
-        const int stage = list ? list[first + i] : i;
-        const int valid = p.valid_k[stage];
+        if ((i & 31) == 0) {
+          const int mine = i + lane;
+          if (mine < cnt[cell]) {
+            const int stage = list ? list[first + mine] : mine;
+            meta_valid = p.valid_k[stage];
+            if (cell == kI8) meta_scale = kscale[stage];
+          }
+        }
+        const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
         const bool phase_first = i == 0 && prev_cell >= 0;
         if (cell == kNv) {
           ok = softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, base_scale,
                                      valid, live_warp, st);
         } else if (cell == kI8) {
-          const float sc = sigma * (q_scale * p.o.k_int8_scale[(int64_t)head * p.stages + stage]);
+          const float sc = sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31));
           ok = softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, sc, valid,
                                      live_warp, st);
         } else {
@@ -592,14 +658,15 @@ int launch(AttnParams& p, int tiles, cudaStream_t st) {
   (void)QB;
   q_region = (q_region + 1023) & ~1023;
   const int fixed = q_region + p_region + D * 4 + (int)sizeof(Barriers) + 128;
-  const int budget = 112 * 1024;  // two CTAs per SM
-  int nslot = (budget - fixed) / slot;
-  nslot = max(2, min(kMaxSlots, nslot));
-  p.nslot = nslot;
-  p.slot_bytes = slot;
+  const int budget = 113 * 1024;  // two CTAs per SM
+  int ring = ((budget - fixed) / 1024) * 1024;
+  ring = max(ring, 2 * ((slot + 127) & ~127));
+  ring = min(ring, kMaxSlots * ((slot + 127) & ~127));
+  p.ring_bytes = ring;
   p.q_region = q_region;
   p.p_region = p_region;
-  const size_t smem = (size_t)fixed + (size_t)nslot * slot;
+  const size_t smem = (size_t)fixed + (size_t)ring;
+  p.debug = getenv("ANEMOI_SM100_DEBUG") ? atoi(getenv("ANEMOI_SM100_DEBUG")) : 0;
   auto kernel = attention_kernel<D>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
