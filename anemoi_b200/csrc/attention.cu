@@ -4,19 +4,24 @@
 // shape) and walks that tile's ragged list of 64-key stages in the order
 // NVFP4 -> INT8 -> FP16 with one online-softmax state.
 //
-// Warp roles (192 threads):
-//   warps 0-3  softmax: thread r owns query row r == TMEM lane r
-//   warp 4     loader: one lane issues 1-D bulk copies (TMA engine) of the Q
-//              record of each phase and of one K|V record per stage into a ring
-//              of shared-memory slots, completion counted on mbarriers
-//   warp 5     MMA: allocates TMEM; one lane issues tcgen05.mma
+// Warp roles (320 threads):
+//   warps 0-7  softmax: warps w and w+4 share TMEM lanes 32*(w%4).. (query rows); each
+//              thread owns half of its row's 64 scores (32 columns) and half of O's
+//              columns; the two threads of a row exchange their partial maximum through
+//              shared memory
+//   warp 8     loader: one lane issues 1-D bulk copies (TMA engine) of the Q record of
+//              each phase and of one K|V record per stage into a ring of shared-memory
+//              slots, completion counted on mbarriers
+//   warp 9     MMA: allocates TMEM; one lane issues tcgen05.mma
 //                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
 //                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
 //              and tcgen05.commit to mbarriers
 // TMEM columns: S [0,64), O [64,64+D), NVFP4 scale factors [192,216).
 // O stays in TMEM across all stages; it is rescaled (read-modify-write by the
 // softmax threads) only when some row's running maximum moved, and at a phase
-// change, where it is also converted between the phases' value domains.
+// change, where it is also converted between the phases' value domains.  P is
+// double-buffered in shared memory for the 4- and 8-bit cells, so the softmax
+// threads only wait for the previous PV when they have to rescale O.
 //
 // Numerics follow the reference's phases
 // (csrc/attention/cuda/sm120/q64_attention_phase_composer.inl:1-146, 506-932,
@@ -30,7 +35,7 @@
 //   FP16 : P -> f16
 // Accumulation is fp32 in TMEM (the reference accumulates a stage in fp16 for the
 // INT8 and FP16 cells).
-#include <cstdlib>
+#include <climits>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
@@ -42,7 +47,10 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kLoaderWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 256;
 constexpr int kColS = 0;
 constexpr int kColO = 64;
@@ -73,13 +81,16 @@ struct AttnParams {
   int ring_bytes;    // key/value ring; re-partitioned into equal slots at every phase
   int q_region;      // bytes
   int p_region;      // bytes
-  int debug;         // TEMP experiment flags
 };
 
 struct Barriers {
   uint64_t kv_full[kMaxSlots];
   uint64_t kv_free[kMaxSlots];
-  uint64_t q_full, q_free, s_full, s_free, p_full, o_done;
+  uint64_t q_full, q_free, s_full, s_free, o_done;
+  uint64_t all_done;  // every MMA of the tile complete (epilogue)
+  // Two P barriers used alternately: a warp that skips the o_done wait may run one stage
+  // ahead, and its arrival must not be counted into the previous stage's phase.
+  uint64_t p_full[2];
   uint32_t tmem_base;
   volatile int abort;
 };
@@ -88,6 +99,29 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Packed two-wide fp32 arithmetic (one instruction for two elements).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
 }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -141,11 +175,12 @@ struct RowState {
   float m, d;
 };
 
-// O[row][c] *= alpha * colf[c] (colf may be null) for the thread's row.
+// O[row][c] *= alpha * colf[c] (colf may be null) for columns [c_begin, c_begin + D/2).
 template <int D>
-__device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const float* colf) {
+__device__ __forceinline__ void rescale_o(uint32_t tmem_row, int c_begin, float alpha,
+                                          const float* colf) {
 #pragma unroll 1
-  for (int c0 = 0; c0 < D; c0 += 32) {
+  for (int c0 = c_begin; c0 < c_begin + D / 2; c0 += 32) {
     uint32_t r[32];
     tmem_ld32(tmem_row + kColO + c0, r);
     tmem_wait_ld();
@@ -160,40 +195,38 @@ __device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const 
   tmem_wait_st();
 }
 
+// Writes the thread's 32 probabilities (keys 32*half .. 32*half+31 of its row) into the
+// K-major P tile in shared memory.
 template <int CELL>
-__device__ __forceinline__ void write_p(uint8_t* p_smem, int row, const float (&p)[64]) {
+__device__ __forceinline__ void write_p(uint8_t* p_tile, int row, int half, const float (&p)[32]) {
   if (CELL == kF16) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 4; ++j) {
       uint4 v;
       __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j * 8 + 2 * i], p[j * 8 + 2 * i + 1]);
-      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 8)) = v;
+      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half * 4 + j, 8)) = v;
     }
   } else if (CELL == kI8) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 2; ++j) {
       uint4 v;
       uint16_t* h = reinterpret_cast<uint16_t*>(&v);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         h[i] = __nv_cvt_float2_to_fp8x2(make_float2(p[j * 16 + 2 * i], p[j * 16 + 2 * i + 1]),
                                         __NV_SATFINITE, __NV_E4M3);
-      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 4)) = v;
+      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half * 2 + j, 4)) = v;
     }
   } else {
+    uint4 v;
+    uint8_t* h = reinterpret_cast<uint8_t*>(&v);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      uint4 v;
-      uint8_t* h = reinterpret_cast<uint8_t*>(&v);
-#pragma unroll
-      for (int i = 0; i < 16; ++i)
-        h[i] = __nv_cvt_float2_to_fp4x2(
-            make_float2(p[j * 32 + 2 * i] * 6.0f, p[j * 32 + 2 * i + 1] * 6.0f), __NV_E2M1,
-            cudaRoundNearest);
-      *reinterpret_cast<uint4*>(p_smem + rec::tile_offset(row, j, 2)) = v;
-    }
+    for (int i = 0; i < 16; ++i)
+      h[i] = __nv_cvt_float2_to_fp4x2(make_float2(p[2 * i], p[2 * i + 1]), __NV_E2M1,
+                                      cudaRoundNearest);  // p already holds 6 P
+    *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half, 2)) = v;
   }
 }
 
@@ -209,90 +242,122 @@ __device__ __forceinline__ float ex2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
 }
 
-// One stage of one phase for the thread's row.  Returns false on an aborted wait.
+// Bytes of one P tile (128 rows x 64 keys) per cell, and which of the two buffers stage g uses.
+__device__ __forceinline__ int p_tile_bytes(int cell) {
+  return cell == kNv ? 128 * 32 : (cell == kI8 ? 128 * 64 : 128 * 128);
+}
+__device__ __forceinline__ int p_buffer(int cell, int g) { return cell == kF16 ? 0 : (g & 1); }
+
+// One stage of one phase for the thread's half row.  Returns false on an aborted wait.
 template <int CELL, int D>
 __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
-                                              const float* colf, uint32_t tmem_row, int row, int g,
-                                              bool phase_first, float score_scale, int valid,
-                                              bool live_warp, RowState& st) {
+                                              const float* colf, uint32_t tmem_row, int row,
+                                              int half, int g, bool phase_first, float score_scale,
+                                              int valid, bool live_warp, RowState& st) {
   if (!wait(b, &b->s_full, g & 1, p.status, 10 + CELL)) return false;
   tc_fence_after_sync();
   if (!live_warp) {
     // padding rows of a 64-row tile: keep the barrier protocol, skip the math
     mbar_arrive(&b->s_free);
-    if (g > 0 && !wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
-    mbar_arrive(&b->p_full);
+    mbar_arrive(&b->p_full[g & 1]);
     return true;
   }
-  float s[64];
+  // The row maximum needs all 64 scores: the other thread's 32 columns are loaded too,
+  // reduced and dropped (TMEM reads are cheap; no exchange through shared memory).
+  float s[32];
+  float mx;
   {
-    uint32_t r0[32], r1[32];
-    tmem_ld32(tmem_row + kColS, r0);
-    tmem_ld32(tmem_row + kColS + 32, r1);
+    uint32_t r[32], o[32];
+    tmem_ld32(tmem_row + kColS + 32 * half, r);
+    tmem_ld32(tmem_row + kColS + 32 * (half ^ 1), o);
     tmem_wait_ld();
+    tc_fence_before_sync();
+    mbar_arrive(&b->s_free);
+    const int mine = valid - 32 * half, theirs = valid - 32 * (half ^ 1);
+    // INT8 cell: as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, a
+    // monotonic map, so the maximum is taken on those floats and 12582912 is
+    // subtracted afterwards (no integer->float conversion instruction).
+    float x[32], y[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (CELL == kI8) {
-        // exact s32 -> f32 for |x| < 2^22 without the conversion unit
-        s[j] = __int_as_float((int)r0[j] + 0x4B400000) - 12582912.0f;
-        s[32 + j] = __int_as_float((int)r1[j] + 0x4B400000) - 12582912.0f;
-      } else {
-        s[j] = __uint_as_float(r0[j]);
-        s[32 + j] = __uint_as_float(r1[j]);
+      x[j] = CELL == kI8 ? __int_as_float((int)r[j] + 0x4B400000) : __uint_as_float(r[j]);
+      y[j] = CELL == kI8 ? __int_as_float((int)o[j] + 0x4B400000) : __uint_as_float(o[j]);
+    }
+    if (valid < 64) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        x[j] = j < mine ? x[j] : -INFINITY;
+        y[j] = j < theirs ? y[j] : -INFINITY;
       }
     }
+    float m0 = max3(y[0], y[1], y[2]), m1 = max3(y[3], y[4], y[5]);
+#pragma unroll
+    for (int j = 6; j < 30; j += 4) {
+      m0 = max3(m0, y[j], y[j + 1]);
+      m1 = max3(m1, y[j + 2], y[j + 3]);
+    }
+    m0 = max3(m0, y[30], y[31]);
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      m0 = max3(m0, x[j], x[j + 1]);
+      m1 = max3(m1, x[j + 2], x[j + 3]);
+    }
+    mx = fmaxf(m0, m1);
+    if (CELL == kI8) mx -= 12582912.0f;   // -inf stays -inf
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[j] = x[j];
   }
-  tc_fence_before_sync();
-  mbar_arrive(&b->s_free);
 
-  if (valid < 64) {
-#pragma unroll
-    for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
-  }
-  float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
-#pragma unroll
-  for (int j = 4; j < 64; j += 2) {
-    mx0 = fmaxf(mx0, s[j]);
-    mx1 = fmaxf(mx1, s[j + 1]);
-  }
-  const float mx = fmaxf(mx0, mx1);
   const float m_new = fmaxf(st.m, mx * score_scale);
   const float alpha = ex2(st.m - m_new);
-  const float bias = CELL == kI8 ? kFp8Offset - m_new : -m_new;
-  float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
-  if (!(p.debug & 4))
+  // exponent = s * scale + bias; the NVFP4 cell produces 6 P directly (e2m1 input range),
+  // the INT8 cell P * 2^8.807 (e4m3 input range); the partial sums are scaled back.
+  const float bias = CELL == kI8 ? kFp8Offset - m_new
+                                 : (CELL == kNv ? 2.5849625007f - m_new : -m_new);
+  const float2 scale2 = make_float2(score_scale, score_scale);
+  // INT8: s holds 12582912 + i; (s - 12582912) * scale + bias with packed ops
+  const float2 bias2 = make_float2(bias, bias);
+  const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
+  float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-  for (int j = 0; j < 64; j += 4) {
-    const float e0 = ex2(fmaf(s[j], score_scale, bias));
-    const float e1 = ex2(fmaf(s[j + 1], score_scale, bias));
-    const float e2 = ex2(fmaf(s[j + 2], score_scale, bias));
-    const float e3 = kPolyShare ? ex2_poly(fmaf(s[j + 3], score_scale, bias))
-                                : ex2(fmaf(s[j + 3], score_scale, bias));
+  for (int j = 0; j < 32; j += 4) {
+    float2 a0 = make_float2(s[j], s[j + 1]), a1 = make_float2(s[j + 2], s[j + 3]);
+    if (CELL == kI8) {
+      a0 = fadd2(a0, magic2);
+      a1 = fadd2(a1, magic2);
+    }
+    a0 = ffma2(a0, scale2, bias2);
+    a1 = ffma2(a1, scale2, bias2);
+    const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x);
+    const float e3 = kPolyShare ? ex2_poly(a1.y) : ex2(a1.y);
     s[j] = e0;
     s[j + 1] = e1;
     s[j + 2] = e2;
     s[j + 3] = e3;
-    sum0 += e0;
-    sum1 += e1;
-    sum2 += e2;
-    sum3 += e3;
+    acc0 = fadd2(acc0, make_float2(e0, e1));
+    acc1 = fadd2(acc1, make_float2(e2, e3));
   }
-  float sum = (sum0 + sum1) + (sum2 + sum3);
-  if (CELL == kI8) sum *= 0.0022326917f;  // 2^-8.807
-  st.d = st.d * alpha + sum;
+  float sum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+  if (CELL == kI8) sum *= 0.0022326917f;   // 2^-8.807
+  if (CELL == kNv) sum *= 0.16666667f;     // 1/6
+  st.d = st.d * alpha + sum;               // partial denominator of this half row
   st.m = m_new;
 
   if (g > 0) {
-    // PV of the previous stage must be complete before P is overwritten or O rescaled.
-    if (!wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
-    tc_fence_after_sync();
     const bool need = phase_first || __any_sync(0xffffffffu, alpha != 1.0f);
-    if (need && !(p.debug & 1)) rescale_o<D>(tmem_row, alpha, phase_first ? colf : nullptr);
+    // O may only be touched once the previous PV is complete.  The single FP16 P
+    // buffer also needs that; the double-buffered 4/8-bit P tiles are free as soon as
+    // this stage's scores arrived (QK of stage g is issued after PV of stage g-2).
+    if (need || CELL == kF16) {
+      if (!wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
+      tc_fence_after_sync();
+    }
+    if (need) rescale_o<D>(tmem_row, half * (D / 2), alpha, phase_first ? colf : nullptr);
   }
-  if (!(p.debug & 2)) write_p<CELL>(p_smem, row, s);
+  write_p<CELL>(p_smem + p_buffer(CELL, g) * p_tile_bytes(CELL), row, half, s);
   fence_proxy_async_smem();
   tc_fence_before_sync();
-  mbar_arrive(&b->p_full);
+  mbar_arrive(&b->p_full[g & 1]);
   return true;
 }
 
@@ -402,15 +467,17 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     mbar_init(&b->q_full, 1);
     mbar_init(&b->q_free, 1);
     mbar_init(&b->s_full, 1);
-    mbar_init(&b->s_free, 128);
-    mbar_init(&b->p_full, 128);
+    mbar_init(&b->s_free, kSoftmaxThreads);
+    mbar_init(&b->p_full[0], kSoftmaxThreads);
+    mbar_init(&b->p_full[1], kSoftmaxThreads);
     mbar_init(&b->o_done, 1);
+    mbar_init(&b->all_done, 1);
     b->abort = 0;
     mbar_init_fence();
   }
   // Query rows beyond QB (64-row tiles padded to the 128-row MMA shape) are never
   // initialised: rows are independent, their results stay in TMEM lanes nobody reads.
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(&b->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -424,7 +491,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : tile);
   const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
 
-  if (warp == 4) {
+  if (warp == kLoaderWarp) {
     // =============================== loader ===============================
     if (lane == 0) {
       int phase_ord = 0;
@@ -477,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         ++phase_ord;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // =============================== MMA issue ===============================
     if (lane == 0) {
       int g = 0, phase_ord = 0;
@@ -516,11 +583,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           if (i > 0) {
             const int gj = g + i - 1;
             const int slot = (i - 1) % nslot;
-            ok = wait(b, &b->p_full, gj & 1, p.status, 6);
+            ok = wait(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t slot_addr = smem_u32(slots + (size_t)slot * slot_bytes);
-            issue_pv<D>(cell, tmem, p_addr, slot_addr, gj > 0);
+            issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
+                        gj > 0);
             mma_commit(&b->o_done);
             mma_commit(&b->kv_free[slot]);
           }
@@ -528,18 +596,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         g += n;
         ++phase_ord;
       }
+      // A softmax warp that skipped o_done waits may be two phases behind on that
+      // barrier, so the end of the tile is signalled on a barrier of its own.
+      if (ok) mma_commit(&b->all_done);
     }
   } else {
     // =============================== softmax rows ===============================
-    const int row = threadIdx.x;
-    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
+    const int half = warp >> 2;                  // which 32 score columns / D/2 output columns
+    const int row = (warp & 3) * 32 + lane;      // query row == TMEM lane
+    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     RowState st{-5.0e6f, 0.0f};
     bool ok = true;
     int g = 0;
     int prev_cell = -1;
     const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
     const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
-    const bool live_warp = warp * 32 < QB;
+    const bool live_warp = (warp & 3) * 32 < QB;
     if (cnt[kNv] > 0) {
       tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
       tmem_wait_st();
@@ -548,15 +620,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       if (cnt[cell] == 0) continue;
       if (prev_cell >= 0) {
         // per-channel factor that moves O from the previous phase's domain into this one's
-        __syncwarp();
-        asm volatile("bar.sync 1, 128;");
-        for (int c = threadIdx.x; c < D; c += 128) {
+        asm volatile("bar.sync 5, 256;" ::: "memory");
+        for (int c = threadIdx.x; c < D; c += kSoftmaxThreads) {
           const float from = prev_cell == kNv ? nv_dom
                                               : (prev_cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f);
           const float to = cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f;
           colf[c] = to == 0.0f ? 0.0f : from / to;
         }
-        asm volatile("bar.sync 1, 128;");
+        asm volatile("bar.sync 5, 256;" ::: "memory");
       }
       const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
       const float q_scale =
@@ -581,28 +652,32 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
         const bool phase_first = i == 0 && prev_cell >= 0;
         if (cell == kNv) {
-          ok = softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, base_scale,
+          ok = softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, base_scale,
                                      valid, live_warp, st);
         } else if (cell == kI8) {
           const float sc = sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31));
-          ok = softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first, sc, valid,
+          ok = softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, sc, valid,
                                      live_warp, st);
         } else {
-          ok = softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, g, phase_first,
+          ok = softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first,
                                       base_scale, valid, live_warp, st);
         }
       }
       prev_cell = cell;
     }
     // ---- epilogue: O_true / d -> fp16, packed row order ----
-    if (ok) ok = wait(b, &b->o_done, (g - 1) & 1, p.status, 7);
-    if (ok) {
+    if (ok) ok = wait(b, &b->all_done, 0, p.status, 7);
+    if (ok && live_warp) {
       tc_fence_after_sync();
-      const float inv = 1.0f / st.d;
+      // partial denominators of the two half rows meet in the (now idle) P tile
+      float* xsum = reinterpret_cast<float*>(p_smem);
+      xsum[half * 128 + row] = st.d;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + (row >> 5)) : "memory");
+      const float inv = 1.0f / (st.d + xsum[(half ^ 1) * 128 + row]);
       const bool live = row < QB;
       __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)tile * QB + row) * D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_row + kColO + c0, r);
         tmem_wait_ld();
@@ -632,7 +707,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int D>
@@ -642,12 +717,12 @@ int launch(AttnParams& p, int tiles, cudaStream_t st) {
   const bool nv = p.s.has_nvfp4 && !p.dense_prefix, f16 = p.s.has_fp16 && !p.dense_prefix;
   if (nv) {
     q_region = max(q_region, 128 * D / 2 + (D / 64) * 512);
-    p_region = max(p_region, 128 * 32);
+    p_region = max(p_region, 2 * 128 * 32);
     slot = max(slot, (int)rec::kv_nvfp4_bytes(D));
   }
   if (p.s.has_int8) {
     q_region = max(q_region, 128 * D);
-    p_region = max(p_region, 128 * 64);
+    p_region = max(p_region, 2 * 128 * 64);
     slot = max(slot, (int)rec::kv_int8_bytes(D));
   }
   if (f16) {
@@ -666,7 +741,6 @@ int launch(AttnParams& p, int tiles, cudaStream_t st) {
   p.q_region = q_region;
   p.p_region = p_region;
   const size_t smem = (size_t)fixed + (size_t)ring;
-  p.debug = getenv("ANEMOI_SM100_DEBUG") ? atoi(getenv("ANEMOI_SM100_DEBUG")) : 0;
   auto kernel = attention_kernel<D>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)

@@ -172,3 +172,27 @@ def test_public_api_matches_executor(run):
         sparse_config=SparseConfig(QB, drop, (), w),
         quant_config=QuantConfig(ratios[0], ratios[1], ratios[2], pkv, pq), calibration=calib)
     assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("index", [1, 2])
+def test_repeated_calls_are_bit_identical(native_library, index):
+    """Run-to-run determinism (40 calls): a lost barrier phase would show up here as a changed
+    warp of output rows."""
+    from anemoi_b200.executor import last_status, sm100_ragged_attention
+
+    name, vs, prefix, H, D, QB, dtype, ratios, drop, w, pkv, pq = CASES[index]
+    f, hh, ww = vs
+    q, k, v = smooth_fields(f, hh, ww, H, D, prefix, seed=1, outliers=(17, 93), dtype=dtype)
+    qd, kd, vd = (t.cuda() for t in (q, k, v))
+    first = None
+    for _ in range(40):
+        out = sm100_ragged_attention(
+            qd, kd, vd, prefix_tokens=prefix, sparsity_ratio=drop, retained_nvfp4_ratio=ratios[0],
+            retained_int8_ratio=ratios[1], retained_fp16_ratio=ratios[2], video_shape=vs, layer=0,
+            query_block_size=QB, prefix_kv_precision=pkv, prefix_query_precision=pq,
+            maxpool_weight=w, nvfp4_scales=(0.01, 0.01, 0.002))
+        if first is None:
+            first = out.clone()
+        else:
+            assert torch.equal(out, first)
+    assert last_status() == 0
