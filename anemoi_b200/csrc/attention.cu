@@ -130,15 +130,20 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-// Bounded wait shared by all roles: gives up after ~2 s or when another thread
-// of the CTA gave up, recording `where` in the status word.
-__device__ __forceinline__ bool wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
+// Bounded wait shared by all roles.  It gives up after ~2 s, or at once when any thread of
+// the CTA already gave up; a give-up records `where` in the status word and sets the CTA's
+// abort flag.  It returns nothing: after an abort every later wait falls through, so each
+// role runs its loops to the end with uniform control flow and the CTA exits normally (its
+// output is invalid, which the status word tells the host).
+template <bool kPark = false>
+__device__ __forceinline__ void wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
                                      int where) {
+  if (mbar_try_wait(bar, parity)) return;
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (b->abort) return false;
-    if ((spin & 1023u) == 1023u) {
+    if (kPark ? mbar_try_wait_hint(bar, parity, 4000u) : mbar_try_wait(bar, parity)) return;
+    if (b->abort) return;
+    if ((spin & (kPark ? 63u : 1023u)) == (kPark ? 63u : 1023u)) {
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > 2000000000ull) break;
@@ -146,7 +151,6 @@ __device__ __forceinline__ bool wait(Barriers* b, uint64_t* bar, uint32_t parity
   }
   b->abort = 1;
   atomicCAS(status, 0, where);
-  return false;
 }
 
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t v) {
@@ -248,19 +252,19 @@ __device__ __forceinline__ int p_tile_bytes(int cell) {
 }
 __device__ __forceinline__ int p_buffer(int cell, int g) { return cell == kF16 ? 0 : (g & 1); }
 
-// One stage of one phase for the thread's half row.  Returns false on an aborted wait.
+// One stage of one phase for the thread's half row.
 template <int CELL, int D>
-__device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
+__device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
                                               const float* colf, uint32_t tmem_row, int row,
                                               int half, int g, bool phase_first, float score_scale,
                                               int valid, bool live_warp, RowState& st) {
-  if (!wait(b, &b->s_full, g & 1, p.status, 10 + CELL)) return false;
+  wait(b, &b->s_full, g & 1, p.status, 10 + CELL);
   tc_fence_after_sync();
   if (!live_warp) {
     // padding rows of a 64-row tile: keep the barrier protocol, skip the math
     mbar_arrive(&b->s_free);
     mbar_arrive(&b->p_full[g & 1]);
-    return true;
+    return;
   }
   // The row maximum needs all 64 scores: the other thread's 32 columns are loaded too,
   // reduced and dropped (TMEM reads are cheap; no exchange through shared memory).
@@ -349,7 +353,7 @@ __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, 
     // buffer also needs that; the double-buffered 4/8-bit P tiles are free as soon as
     // this stage's scores arrived (QK of stage g is issued after PV of stage g-2).
     if (need || CELL == kF16) {
-      if (!wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL)) return false;
+      wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL);
       tc_fence_after_sync();
     }
     if (need) rescale_o<D>(tmem_row, half * (D / 2), alpha, phase_first ? colf : nullptr);
@@ -358,7 +362,6 @@ __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, 
   fence_proxy_async_smem();
   tc_fence_before_sync();
   mbar_arrive(&b->p_full[g & 1]);
-  return true;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -366,39 +369,40 @@ __device__ __forceinline__ bool softmax_stage(Barriers* b, const AttnParams& p, 
 // ------------------------------------------------------------------------------------------
 template <int D>
 __device__ __forceinline__ void issue_qk(int cell, uint32_t tmem, uint32_t q_addr, uint32_t k_addr,
-                                         uint32_t kv_slot_addr) {
+                                         uint32_t kv_slot_addr, uint32_t issue) {
   if (cell == kF16) {
     constexpr uint32_t chunks = D / 8;
     const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 16; ++k)
       mma_f16_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
-                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else if (cell == kI8) {
     constexpr uint32_t chunks = D / 16;
     const uint32_t idesc = instr_desc(kFmtS8, kFmtS8, kAccS32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 32; ++k)
       mma_i8_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
-                smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+                smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else {
     constexpr uint32_t chunks = D / 32;
     const uint32_t idesc = instr_desc_nvf4(128, 64);
     const uint32_t ksf = kv_slot_addr + rec::kv_nvfp4_ksf_offset(D);
 #pragma unroll
     for (int k = 0; k < D / 64; ++k)
-      tmem_cp_32x128b_warpx4(tmem + kColSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128));
+      tmem_cp_32x128b_warpx4(tmem + kColSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128), issue);
 #pragma unroll
     for (int k = 0; k < D / 64; ++k)
       mma_nvf4_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
                   smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0,
-                  tmem + kColSfaQ + 4 * k, tmem + kColSfbK + 4 * k);
+                  tmem + kColSfaQ + 4 * k, tmem + kColSfbK + 4 * k, issue);
   }
 }
 
 template <int D>
 __device__ __forceinline__ void issue_pv(int cell, uint32_t tmem, uint32_t p_addr,
-                                         uint32_t kv_slot_addr, uint32_t accumulate) {
+                                         uint32_t kv_slot_addr, uint32_t accumulate,
+                                         uint32_t issue) {
   if (cell == kF16) {
     const uint32_t v_addr = kv_slot_addr + 64 * D * 2;
     const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, D, 0, 1);
@@ -406,21 +410,21 @@ __device__ __forceinline__ void issue_pv(int cell, uint32_t tmem, uint32_t p_add
 #pragma unroll
     for (int k = 0; k < 4; ++k)
       mma_f16_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 8 * 128),
-                 smem_desc(v_addr + k * 2 * v_lbo, v_lbo, 128), idesc, accumulate | (k > 0));
+                 smem_desc(v_addr + k * 2 * v_lbo, v_lbo, 128), idesc, accumulate | (k > 0), issue);
   } else if (cell == kI8) {
     const uint32_t v_addr = kv_slot_addr + 64 * D;
     const uint32_t idesc = instr_desc(kFmtE4M3, kFmtE4M3, kAccF32, 128, D, 0, 0);
 #pragma unroll
     for (int k = 0; k < 2; ++k)
       mma_f8_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 4 * 128),
-                smem_desc(v_addr + k * 256, 128, 4 * 128), idesc, accumulate | (k > 0));
+                smem_desc(v_addr + k * 256, 128, 4 * 128), idesc, accumulate | (k > 0), issue);
   } else {
     const uint32_t v_addr = kv_slot_addr + rec::kv_nvfp4_v_offset(D);
     const uint32_t vsf = kv_slot_addr + rec::kv_nvfp4_vsf_offset(D);
     const uint32_t idesc = instr_desc_nvf4(128, D);
-    tmem_cp_32x128b_warpx4(tmem + kColSfbV, smem_desc(vsf, 128, 128));
+    tmem_cp_32x128b_warpx4(tmem + kColSfbV, smem_desc(vsf, 128, 128), issue);
     mma_nvf4_ss(tmem + kColO, smem_desc(p_addr, 128, 2 * 128), smem_desc(v_addr, 128, 2 * 128),
-                idesc, accumulate, tmem + kColSfaP, tmem + kColSfbV);
+                idesc, accumulate, tmem + kColSfaP, tmem + kColSfbV, issue);
   }
 }
 
@@ -493,120 +497,118 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
 
   if (warp == kLoaderWarp) {
     // =============================== loader ===============================
-    if (lane == 0) {
-      int phase_ord = 0;
-      uint32_t filled = 0, fillpar = 0;  // per slot: ever filled / parity of the fill count
-      bool ok = true;
-      for (int cell = 0; cell < 3 && ok; ++cell) {
-        if (cnt[cell] == 0) continue;
-        if (phase_ord > 0) ok = wait(b, &b->q_free, (phase_ord - 1) & 1, p.status, 1);
-        if (!ok) break;
-        const int qbytes = CellInfo<D>::q_bytes(cell, QB);
-        const uint8_t* qsrc =
-            cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
-            : cell == kI8 ? static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes
-                          : static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes;
-        mbar_arrive_expect_tx(&b->q_full, qbytes);
-        if (cell == kNv && QB == 64) {
-          // codes fill the first half of the 128-row tile; scale blocks follow the full tile
-          const int codes = QB * D / 2;
-          bulk_g2s(q_smem, qsrc, codes, &b->q_full);
-          bulk_g2s(q_smem + 128 * D / 2, qsrc + codes, qbytes - codes, &b->q_full);
-        } else {
-          bulk_g2s(q_smem, qsrc, qbytes, &b->q_full);
-        }
-        const int kvbytes = CellInfo<D>::kv_bytes(cell);
-        const uint8_t* kvbase =
-            (cell == kNv ? static_cast<const uint8_t*>(p.o.kv_nvfp4)
-             : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
-                           : static_cast<const uint8_t*>(p.o.kv_fp16)) +
-            (int64_t)head * p.stages * kvbytes;
-        const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
-        // The ring is cut into equal slots of this phase's record size; slots of the
-        // previous phase must all be released before the new geometry is written.
-        const int slot_bytes = (kvbytes + 127) & ~127;
-        const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
-        for (int sl = 0; sl < kMaxSlots && ok; ++sl)
-          if ((filled >> sl) & 1u)
-            ok = wait(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
-        for (int i = 0; i < cnt[cell] && ok; ++i) {
-          const int slot = i % nslot;
-          if ((filled >> slot) & 1u)
-            ok = wait(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
-          if (!ok) break;
-          const int stage = list ? list[first + i] : i;
-          mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes);
-          bulk_g2s(slots + (size_t)slot * slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
-                   &b->kv_full[slot]);
-          filled |= 1u << slot;
-          fillpar ^= 1u << slot;
-        }
-        ++phase_ord;
+    // The whole warp walks the list with uniform control flow; one lane issues.
+    const uint32_t lead = lane == 0;
+    int phase_ord = 0;
+    uint32_t filled = 0, fillpar = 0;  // per slot: ever filled / parity of the fill count
+    for (int cell = 0; cell < 3; ++cell) {
+      if (cnt[cell] == 0) continue;
+      if (phase_ord > 0) wait<true>(b, &b->q_free, (phase_ord - 1) & 1, p.status, 1);
+      const int qbytes = CellInfo<D>::q_bytes(cell, QB);
+      const uint8_t* qsrc =
+          cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
+          : cell == kI8 ? static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes
+                        : static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes;
+      mbar_arrive_expect_tx(&b->q_full, qbytes, lead);
+      if (cell == kNv && QB == 64) {
+        // codes fill the first half of the 128-row tile; scale blocks follow the full tile
+        const int codes = QB * D / 2;
+        bulk_g2s(q_smem, qsrc, codes, &b->q_full, lead);
+        bulk_g2s(q_smem + 128 * D / 2, qsrc + codes, qbytes - codes, &b->q_full, lead);
+      } else {
+        bulk_g2s(q_smem, qsrc, qbytes, &b->q_full, lead);
       }
+      const int kvbytes = CellInfo<D>::kv_bytes(cell);
+      const uint8_t* kvbase =
+          (cell == kNv ? static_cast<const uint8_t*>(p.o.kv_nvfp4)
+           : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
+                         : static_cast<const uint8_t*>(p.o.kv_fp16)) +
+          (int64_t)head * p.stages * kvbytes;
+      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      // The ring is cut into equal slots of this phase's record size; slots of the
+      // previous phase must all be released before the new geometry is written.
+      const int slot_bytes = (kvbytes + 127) & ~127;
+      const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
+      for (int sl = 0; sl < kMaxSlots; ++sl)
+        if ((filled >> sl) & 1u)
+          wait<true>(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
+      int stage_l = 0;  // list entries, 32 at a time, one per lane
+      for (int i = 0; i < cnt[cell]; ++i) {
+        if ((i & 31) == 0 && list != nullptr && i + lane < cnt[cell])
+          stage_l = list[first + i + lane];
+        const int stage = list ? __shfl_sync(0xffffffffu, stage_l, i & 31) : i;
+        const int slot = i % nslot;
+        if ((filled >> slot) & 1u)
+          wait<true>(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
+        mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes, lead);
+        bulk_g2s(slots + (size_t)slot * slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
+                 &b->kv_full[slot], lead);
+        filled |= 1u << slot;
+        fillpar ^= 1u << slot;
+      }
+      ++phase_ord;
     }
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ===============================
-    if (lane == 0) {
-      int g = 0, phase_ord = 0;
-      uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
-      bool ok = true;
-      const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
-      for (int cell = 0; cell < 3 && ok; ++cell) {
-        if (cnt[cell] == 0) continue;
-        ok = wait(b, &b->q_full, phase_ord & 1, p.status, 3);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (cell == kNv) {
-          const uint32_t qsf = q_addr + 128 * D / 2;
+    // Uniform control flow for the whole warp (descriptors stay warp-uniform values);
+    // only the tcgen05 instructions themselves are predicated on one lane.
+    const uint32_t lead = lane == 0;
+    int g = 0, phase_ord = 0;
+    uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
+    const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+    for (int cell = 0; cell < 3; ++cell) {
+      if (cnt[cell] == 0) continue;
+      wait<true>(b, &b->q_full, phase_ord & 1, p.status, 3);
+      tc_fence_after_sync();
+      if (cell == kNv) {
+        const uint32_t qsf = q_addr + 128 * D / 2;
 #pragma unroll
-          for (int k = 0; k < D / 64; ++k)
-            tmem_cp_32x128b_warpx4(tmem + kColSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128));
-        }
-        const int n = cnt[cell];
-        const int slot_bytes = (CellInfo<D>::kv_bytes(cell) + 127) & ~127;
-        const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
-        // software pipeline: QK of stage i+1 is issued before PV of stage i
-        for (int i = 0; i <= n && ok; ++i) {
-          if (i < n) {
-            const int gi = g + i;
-            const int slot = i % nslot;
-            ok = wait(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
-            usepar ^= 1u << slot;
-            if (ok && gi > 0) ok = wait(b, &b->s_free, (gi - 1) & 1, p.status, 5);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * slot_bytes);
-            issue_qk<D>(cell, tmem, q_addr, slot_addr, slot_addr);
-            mma_commit(&b->s_full);
-            if (i == n - 1) mma_commit(&b->q_free);
-          }
-          if (i > 0) {
-            const int gj = g + i - 1;
-            const int slot = (i - 1) % nslot;
-            ok = wait(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t slot_addr = smem_u32(slots + (size_t)slot * slot_bytes);
-            issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
-                        gj > 0);
-            mma_commit(&b->o_done);
-            mma_commit(&b->kv_free[slot]);
-          }
-        }
-        g += n;
-        ++phase_ord;
+        for (int k = 0; k < D / 64; ++k)
+          tmem_cp_32x128b_warpx4(tmem + kColSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128),
+                                 lead);
       }
-      // A softmax warp that skipped o_done waits may be two phases behind on that
-      // barrier, so the end of the tile is signalled on a barrier of its own.
-      if (ok) mma_commit(&b->all_done);
+      const int n = cnt[cell];
+      const int slot_bytes = (CellInfo<D>::kv_bytes(cell) + 127) & ~127;
+      const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
+      const uint32_t ring_addr = smem_u32(slots);
+      // software pipeline: QK of stage i+1 is issued before PV of stage i
+      for (int i = 0; i <= n; ++i) {
+        if (i < n) {
+          const int gi = g + i;
+          const int slot = i % nslot;
+          wait<true>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
+          usepar ^= 1u << slot;
+          if (gi > 0) wait<true>(b, &b->s_free, (gi - 1) & 1, p.status, 5);
+          tc_fence_after_sync();
+          const uint32_t slot_addr = ring_addr + slot * slot_bytes;
+          issue_qk<D>(cell, tmem, q_addr, slot_addr, slot_addr, lead);
+          mma_commit(&b->s_full, lead);
+          if (i == n - 1) mma_commit(&b->q_free, lead);
+        }
+        if (i > 0) {
+          const int gj = g + i - 1;
+          const int slot = (i - 1) % nslot;
+          wait<true>(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
+          tc_fence_after_sync();
+          const uint32_t slot_addr = ring_addr + slot * slot_bytes;
+          issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
+                      gj > 0, lead);
+          mma_commit(&b->o_done, lead);
+          mma_commit(&b->kv_free[slot], lead);
+        }
+      }
+      g += n;
+      ++phase_ord;
     }
+    // A softmax warp that skipped o_done waits may be two phases behind on that barrier,
+    // so the end of the tile is signalled on a barrier of its own.
+    mma_commit(&b->all_done, lead);
   } else {
     // =============================== softmax rows ===============================
     const int half = warp >> 2;                  // which 32 score columns / D/2 output columns
     const int row = (warp & 3) * 32 + lane;      // query row == TMEM lane
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     RowState st{-5.0e6f, 0.0f};
-    bool ok = true;
     int g = 0;
     int prev_cell = -1;
     const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
@@ -616,7 +618,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
       tmem_wait_st();
     }
-    for (int cell = 0; cell < 3 && ok; ++cell) {
+    for (int cell = 0; cell < 3; ++cell) {
       if (cnt[cell] == 0) continue;
       if (prev_cell >= 0) {
         // per-channel factor that moves O from the previous phase's domain into this one's
@@ -640,7 +642,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       int meta_valid = 64;
       float meta_scale = 1.0f;
       const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
-      for (int i = 0; i < cnt[cell] && ok; ++i, ++g) {
+      for (int i = 0; i < cnt[cell]; ++i, ++g) {
         if ((i & 31) == 0) {
           const int mine = i + lane;
           if (mine < cnt[cell]) {
@@ -652,22 +654,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
         const bool phase_first = i == 0 && prev_cell >= 0;
         if (cell == kNv) {
-          ok = softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, base_scale,
+          softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, base_scale,
                                      valid, live_warp, st);
         } else if (cell == kI8) {
           const float sc = sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31));
-          ok = softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, sc, valid,
+          softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, sc, valid,
                                      live_warp, st);
         } else {
-          ok = softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first,
+          softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first,
                                       base_scale, valid, live_warp, st);
         }
       }
       prev_cell = cell;
     }
     // ---- epilogue: O_true / d -> fp16, packed row order ----
-    if (ok) ok = wait(b, &b->all_done, 0, p.status, 7);
-    if (ok && live_warp) {
+    wait(b, &b->all_done, 0, p.status, 7);
+    if (live_warp) {
       tc_fence_after_sync();
       // partial denominators of the two half rows meet in the (now idle) P tile
       float* xsum = reinterpret_cast<float*>(p_smem);

@@ -248,6 +248,7 @@ __device__ __forceinline__ void write_pools(const __half* tile, int rows, int co
   if (threadIdx.x < D) {
     const int c = threadIdx.x;
     float sum = 0.0f, mx = -INFINITY;
+#pragma unroll 8
     for (int r = 0; r < rows; ++r) {
       const float x = __half2float(tile[r * (D + kPad) + c]);
       sum = __fadd_rn(sum, x);
@@ -266,8 +267,10 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
   __shared__ float recip[D];
 
   const int R = p.s.video_blocks;
-  const int head = blockIdx.y;
-  const int task = blockIdx.x;
+  // heads vary fastest across concurrently running CTAs: neighbours read adjacent 2*D-byte
+  // pieces of the same token rows
+  const int head = blockIdx.x;
+  const int task = blockIdx.y;
   constexpr int kF = QB / 64;
   const InT* q = static_cast<const InT*>(p.q);
   const InT* k = static_cast<const InT*>(p.k);
@@ -417,7 +420,9 @@ int launch(const PrepParams& p, cudaStream_t stream) {
         static_cast<const InT*>(p.v), reinterpret_cast<int*>(p.o.v_amax), p.s.seq_tokens,
         p.s.heads, D / 8, p.stride[4], p.stride[5], tokens_per_block);
   }
-  dim3 grid(2 * p.s.video_blocks + p.prefix_stages + p.prefix_q_tiles, p.s.heads);
+  const int tasks = 2 * p.s.video_blocks + p.prefix_stages + p.prefix_q_tiles;
+  if (tasks > 65535) return ANEMOI_SM100_ELIMIT;
+  dim3 grid(p.s.heads, tasks);
   kernel<<<grid, kThreads, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
