@@ -316,3 +316,48 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
       prefix_phase, list_capacity, row_offset, row_counts, stage_ids);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
+
+// ------------------------------------------------------------------------------------------
+// Routing without any allocation by the caller
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library cannot hand it scratch memory: a serving loop whose memory
+// pool is frozen after start-up, or code that must not call cudaMalloc because it runs
+// between other streams' work and cannot afford the implicit device synchronisation.
+// For them the scratch of anemoi_sm100_route lives in this file-scope device array.
+// Every GPU that loads the library holds these 8 MiB until the process exits.
+constexpr int64_t kStaticScratchInts = 2 * 1024 * 1024;  // 8 MiB of int32
+static __device__ __align__(256) int g_route_scratch[kStaticScratchInts];
+
+namespace {
+constexpr int kMaxDevices = 64;
+int* g_route_scratch_address[kMaxDevices];  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int64_t anemoi_sm100_route_static_max_bytes(void) { return kStaticScratchInts * 4; }
+
+extern "C" int anemoi_sm100_route_static(const anemoi_sm100_shape* shape, const void* probability,
+                                         int64_t n16, int64_t n8, int64_t n4, int prefix_phase,
+                                         int32_t* row_offset, int32_t* row_counts,
+                                         int32_t* stage_ids, int64_t list_capacity,
+                                         void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
+  const int64_t need = scratch_ints(shape->heads, shape->video_blocks);
+  if (need > kStaticScratchInts) return ANEMOI_SM100_ELIMIT;  // heads*(32777 + 4*blocks) ints
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return ANEMOI_SM100_ELAUNCH;
+  // In host code the array's name is only a stand-in for the symbol, not a device address.
+  // The address is looked up once per device, with that device current (the first call on
+  // a device does it, so make that call before any stream capture), and then reused.
+  int* scratch = g_route_scratch_address[device];
+  if (scratch == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_route_scratch) != cudaSuccess ||
+        scratch == nullptr)
+      return ANEMOI_SM100_ELAUNCH;
+    g_route_scratch_address[device] = scratch;
+  }
+  // Same kernels as anemoi_sm100_route; the bins and cursors that must start at zero are
+  // cleared there on `stream` at every call, the rest is overwritten before it is read.
+  return anemoi_sm100_route(shape, probability, n16, n8, n4, prefix_phase, scratch, need * 4,
+                            row_offset, row_counts, stage_ids, list_capacity, stream);
+}

@@ -76,6 +76,8 @@ def library() -> C.CDLL:
         "anemoi_sm100_route_scratch_bytes": (I64, [SP]),
         "anemoi_sm100_route_list_capacity": (I64, [SP, I64, I64, I64, C.c_int]),
         "anemoi_sm100_route": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, I64, P, P, P, I64, P]),
+        "anemoi_sm100_route_static_max_bytes": (I64, []),
+        "anemoi_sm100_route_static": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, P, I64, P]),
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
         "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
@@ -94,7 +96,8 @@ def library() -> C.CDLL:
 EXPORTED = (
     "anemoi_sm100_arch", "anemoi_sm100_operand_bytes", "anemoi_sm100_prepare",
     "anemoi_sm100_draft_probability", "anemoi_sm100_route_scratch_bytes",
-    "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_attention",
+    "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
+    "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads",
 )
@@ -213,6 +216,21 @@ def route(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_p
                                   _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,
                                   _stream(dev)), "anemoi_sm100_route")
     return lists
+
+
+def route_static(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_phase: int,
+                 lists: RouteLists) -> None:
+    """Routing into caller-owned ``lists`` with the library's built-in scratch array.
+
+    For hosts that may not allocate on their request path: nothing is allocated here or in
+    the library.  All calls on a device share one scratch array, so keep them on one stream
+    (or order them with events); the first call on a device should precede stream capture."""
+    if not shape.prefix_tokens:
+        prefix_phase = -1
+    _check(library().anemoi_sm100_route_static(
+        C.byref(shape), _ptr(prob), n16, n8, n4, prefix_phase, _ptr(lists.row_offset),
+        _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity, _stream(prob.device)),
+        "anemoi_sm100_route_static")
 
 
 def attention(shape: Shape, store: OperandStore, lists: RouteLists, valid_k: torch.Tensor,

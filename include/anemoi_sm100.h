@@ -132,6 +132,25 @@ int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* probability,
                        int64_t scratch_bytes, int32_t* row_offset, int32_t* row_counts,
                        int32_t* stage_ids, int64_t list_capacity, void* stream);
 
+/* Routing for callers that cannot provide scratch memory.  It has no counterpart in the
+ * reference.  A host whose memory pool is fixed once it starts serving, or that must avoid
+ * cudaMalloc / cudaFree on its request path (they synchronise the whole device), cannot
+ * size and pass the scratch buffer anemoi_sm100_route needs.  This variant does the same
+ * work with the same arguments and results, but its scratch is an 8 MiB array that is part
+ * of the library image (held on every GPU that loads the library until the process ends);
+ * it calls no allocating routine of any kind.  Shapes that need more scratch than that -
+ * heads * (32777 + 4 * video_blocks) * 4 bytes > anemoi_sm100_route_static_max_bytes() -
+ * are refused with ANEMOI_SM100_ELIMIT.  The first call on a device looks up the array's
+ * device address; make that call outside any stream capture.  All calls on a device share
+ * the one array (it keeps the last call's contents; what must start at zero is cleared on
+ * `stream` at every call), so two calls whose kernels may overlap on the GPU race: issue
+ * them on one stream or order them with events. */
+int64_t anemoi_sm100_route_static_max_bytes(void);
+int anemoi_sm100_route_static(const anemoi_sm100_shape* shape, const void* probability,
+                              int64_t n16, int64_t n8, int64_t n4, int prefix_phase,
+                              int32_t* row_offset, int32_t* row_counts, int32_t* stage_ids,
+                              int64_t list_capacity, void* stream);
+
 /* Block-sparse mixed-precision flash attention of the video query blocks.
  *   valid_k      int32 [stages] real keys per stage
  *   out_packed   fp16 [H][R*QB][D] packed row order; rows of empty lists are not written
