@@ -1,0 +1,47 @@
+"""GPU (2 or more devices): the head-sharded Ulysses run equals the single-GPU run bit for bit."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from anemoi_b200 import (NVFP4Calibration, QuantConfig, SparseConfig, VisualLayout,
+                                 anemoi_attention, ulysses)
+        from tests.helpers import smooth_fields
+
+        heads, prefix, vs = 4 * world, 37, (2, 12, 20)
+        q, k, v = smooth_fields(*vs, heads, 128, prefix, seed=3, outliers=(17, 93), dtype=torch.bfloat16)
+        kw = dict(layout=VisualLayout(vs, prefix), layer=0, sparse_config=SparseConfig(128, 0.6, (), 0.5),
+                  quant_config=QuantConfig(0.4, 0.4, 0.2), calibration=NVFP4Calibration(0.01, 0.01, 0.002))
+        full = anemoi_attention(q.cuda(), k.cuda(), v.cuda(), **kw)
+        rows = ulysses.shard_rows(q.size(1), world)      # uneven: 517 tokens
+        lo = sum(rows[:rank])
+        mine = [t[:, lo : lo + rows[rank]].contiguous().cuda() for t in (q, k, v)]
+        got = ulysses.ulysses_anemoi_attention(*mine, **kw)
+        torch.cuda.synchronize()
+        results[rank] = bool(torch.equal(got, full[:, lo : lo + rows[rank]]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_run_equals_single_gpu(native_library):
+    world = min(torch.cuda.device_count(), 2)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    results = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {r: True for r in range(world)}
