@@ -16,7 +16,9 @@
 //                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
 //                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
 //              and tcgen05.commit to mbarriers
-// TMEM columns: S [0,64), O [64,64+D), NVFP4 scale factors [192,216).
+// TMEM columns: S0 [0,64), O [64,64+D), and [192,256) holds the NVFP4 scale factors in the
+// NVFP4 phase and a second score buffer S1 in the INT8 / FP16 phases (QK of stage g+1 runs
+// while the softmax threads still read the scores of stage g).
 // O stays in TMEM across all stages; it is rescaled (read-modify-write by the
 // softmax threads) only when some row's running maximum moved, and at a phase
 // change, where it is also converted between the phases' value domains.  P is
@@ -53,6 +55,7 @@ constexpr int kLoaderWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTmemCols = 256;
 constexpr int kColS = 0;
+constexpr int kColS1 = 192;  // second score buffer; aliases the scale-factor columns
 constexpr int kColO = 64;
 constexpr int kColSfaQ = 192;  // 2 k-steps x 4 columns
 constexpr int kColSfbK = 200;  // 2 k-steps x 4 columns
@@ -86,9 +89,10 @@ struct AttnParams {
 struct Barriers {
   uint64_t kv_full[kMaxSlots];
   uint64_t kv_free[kMaxSlots];
-  uint64_t q_full, q_free, s_full, s_free, o_done;
+  uint64_t q_full, q_free;
+  uint64_t s_full[2], s_free[2];  // per score buffer
   uint64_t all_done;  // every MMA of the tile complete (epilogue)
-  // Two P barriers used alternately: a warp that skips the o_done wait may run one stage
+  // Two P barriers used alternately: a warp that skips the wait for the previous PV may run one stage
   // ahead, and its arrival must not be counted into the previous stage's phase.
   uint64_t p_full[2];
   uint32_t tmem_base;
@@ -135,10 +139,9 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // abort flag.  It returns nothing: after an abort every later wait falls through, so each
 // role runs its loops to the end with uniform control flow and the CTA exits normally (its
 // output is invalid, which the status word tells the host).
-template <bool kPark = false>
-__device__ __forceinline__ void wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
-                                     int where) {
-  if (mbar_try_wait(bar, parity)) return;
+template <bool kPark>
+__device__ __noinline__ void wait_slow(Barriers* b, uint64_t* bar, uint32_t parity,
+                                       int32_t* status, int where) {
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if (kPark ? mbar_try_wait_hint(bar, parity, 4000u) : mbar_try_wait(bar, parity)) return;
@@ -151,6 +154,14 @@ __device__ __forceinline__ void wait(Barriers* b, uint64_t* bar, uint32_t parity
   }
   b->abort = 1;
   atomicCAS(status, 0, where);
+}
+
+// One inline poll; the bounded spin loop is a shared out-of-line function (code size).
+template <bool kPark = false>
+__device__ __forceinline__ void wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
+                                     int where) {
+  if (mbar_try_wait(bar, parity)) return;
+  wait_slow<kPark>(b, bar, parity, status, where);
 }
 
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t v) {
@@ -251,85 +262,95 @@ __device__ __forceinline__ int p_tile_bytes(int cell) {
   return cell == kNv ? 128 * 32 : (cell == kI8 ? 128 * 64 : 128 * 128);
 }
 __device__ __forceinline__ int p_buffer(int cell, int g) { return cell == kF16 ? 0 : (g & 1); }
+// Score buffer of stage g: the NVFP4 phase has a single one (the other holds its scale factors).
+__device__ __forceinline__ int s_buffer(int cell, int g) { return cell == kNv ? 0 : (g & 1); }
+__device__ __forceinline__ uint32_t s_column(int sb) { return sb ? kColS1 : kColS; }
 
-// One stage of one phase for the thread's half row.
-template <int CELL, int D>
-__device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
-                                              const float* colf, uint32_t tmem_row, int row,
-                                              int half, int g, bool phase_first, float score_scale,
-                                              int valid, bool live_warp, RowState& st) {
-  wait(b, &b->s_full, g & 1, p.status, 10 + CELL);
+// One stage of one phase for the thread's half row.  A single copy of this code serves the
+// three cells (the cell is a run-time argument and the function is not inlined): the kernel's
+// hot code has to stay well inside the instruction cache, and three unrolled copies did not.
+template <int D>
+__device__ __noinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
+                                           const float* colf, uint32_t tmem_row, int row, int half,
+                                           int cell, int g, bool phase_first, float score_scale,
+                                           int valid, bool live_warp, int sb, uint32_t s_parity,
+                                           uint64_t* prev_pv_bar, uint32_t prev_pv_parity,
+                                           RowState& st) {
+  wait(b, &b->s_full[sb], s_parity, p.status, 10 + cell);
   tc_fence_after_sync();
   if (!live_warp) {
     // padding rows of a 64-row tile: keep the barrier protocol, skip the math
-    mbar_arrive(&b->s_free);
+    mbar_arrive(&b->s_free[sb]);
     mbar_arrive(&b->p_full[g & 1]);
     return;
   }
-  // The row maximum needs all 64 scores: the other thread's 32 columns are loaded too,
-  // reduced and dropped (TMEM reads are cheap; no exchange through shared memory).
+  // INT8 cell: scores are s32; as_float(i + 0x4B400000) == 12582912 + i exactly for
+  // |i| < 2^22, a monotonic map, so the maximum is taken on those floats and 12582912 is
+  // subtracted afterwards (no integer->float conversion instruction).  The other cells add 0.
+  const int to_float = cell == kI8 ? 0x4B400000 : 0;
+  const float magic = cell == kI8 ? -12582912.0f : 0.0f;
+  // The row maximum needs all 64 scores: the other thread's 32 columns are loaded first,
+  // reduced to one value and dropped (TMEM reads are cheap; no exchange through shared
+  // memory), then the thread's own 32 columns.
   float s[32];
   float mx;
   {
-    uint32_t r[32], o[32];
-    tmem_ld32(tmem_row + kColS + 32 * half, r);
-    tmem_ld32(tmem_row + kColS + 32 * (half ^ 1), o);
+    const int mine = valid - 32 * half, theirs = valid - 32 * (half ^ 1);
+    float m0, m1;
+    {
+      uint32_t o[32];
+      tmem_ld32(tmem_row + s_column(sb) + 32 * (half ^ 1), o);
+      tmem_wait_ld();
+      float y[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) y[j] = __int_as_float((int)o[j] + to_float);
+      if (theirs < 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = j < theirs ? y[j] : -INFINITY;
+      }
+      m0 = max3(y[0], y[1], y[2]);
+      m1 = max3(y[3], y[4], y[5]);
+#pragma unroll
+      for (int j = 6; j < 30; j += 4) {
+        m0 = max3(m0, y[j], y[j + 1]);
+        m1 = max3(m1, y[j + 2], y[j + 3]);
+      }
+      m0 = max3(m0, y[30], y[31]);
+    }
+    uint32_t r[32];
+    tmem_ld32(tmem_row + s_column(sb) + 32 * half, r);
     tmem_wait_ld();
     tc_fence_before_sync();
-    mbar_arrive(&b->s_free);
-    const int mine = valid - 32 * half, theirs = valid - 32 * (half ^ 1);
-    // INT8 cell: as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, a
-    // monotonic map, so the maximum is taken on those floats and 12582912 is
-    // subtracted afterwards (no integer->float conversion instruction).
-    float x[32], y[32];
+    mbar_arrive(&b->s_free[sb]);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      x[j] = CELL == kI8 ? __int_as_float((int)r[j] + 0x4B400000) : __uint_as_float(r[j]);
-      y[j] = CELL == kI8 ? __int_as_float((int)o[j] + 0x4B400000) : __uint_as_float(o[j]);
-    }
-    if (valid < 64) {
+    for (int j = 0; j < 32; ++j) s[j] = __int_as_float((int)r[j] + to_float);
+    if (mine < 32) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        x[j] = j < mine ? x[j] : -INFINITY;
-        y[j] = j < theirs ? y[j] : -INFINITY;
-      }
+      for (int j = 0; j < 32; ++j) s[j] = j < mine ? s[j] : -INFINITY;
     }
-    float m0 = max3(y[0], y[1], y[2]), m1 = max3(y[3], y[4], y[5]);
-#pragma unroll
-    for (int j = 6; j < 30; j += 4) {
-      m0 = max3(m0, y[j], y[j + 1]);
-      m1 = max3(m1, y[j + 2], y[j + 3]);
-    }
-    m0 = max3(m0, y[30], y[31]);
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-      m0 = max3(m0, x[j], x[j + 1]);
-      m1 = max3(m1, x[j + 2], x[j + 3]);
+      m0 = max3(m0, s[j], s[j + 1]);
+      m1 = max3(m1, s[j + 2], s[j + 3]);
     }
-    mx = fmaxf(m0, m1);
-    if (CELL == kI8) mx -= 12582912.0f;   // -inf stays -inf
-#pragma unroll
-    for (int j = 0; j < 32; ++j) s[j] = x[j];
+    mx = fmaxf(m0, m1) + magic;   // -inf stays -inf
   }
 
   const float m_new = fmaxf(st.m, mx * score_scale);
   const float alpha = ex2(st.m - m_new);
   // exponent = s * scale + bias; the NVFP4 cell produces 6 P directly (e2m1 input range),
   // the INT8 cell P * 2^8.807 (e4m3 input range); the partial sums are scaled back.
-  const float bias = CELL == kI8 ? kFp8Offset - m_new
-                                 : (CELL == kNv ? 2.5849625007f - m_new : -m_new);
+  const float bias = cell == kI8 ? kFp8Offset - m_new
+                                 : (cell == kNv ? 2.5849625007f - m_new : -m_new);
+  const float sum_scale = cell == kI8 ? 0.0022326917f : (cell == kNv ? 0.16666667f : 1.0f);
   const float2 scale2 = make_float2(score_scale, score_scale);
-  // INT8: s holds 12582912 + i; (s - 12582912) * scale + bias with packed ops
   const float2 bias2 = make_float2(bias, bias);
-  const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
+  const float2 magic2 = make_float2(magic, magic);
   float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
-    float2 a0 = make_float2(s[j], s[j + 1]), a1 = make_float2(s[j + 2], s[j + 3]);
-    if (CELL == kI8) {
-      a0 = fadd2(a0, magic2);
-      a1 = fadd2(a1, magic2);
-    }
+    float2 a0 = fadd2(make_float2(s[j], s[j + 1]), magic2);
+    float2 a1 = fadd2(make_float2(s[j + 2], s[j + 3]), magic2);
     a0 = ffma2(a0, scale2, bias2);
     a1 = ffma2(a1, scale2, bias2);
     const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x);
@@ -341,9 +362,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     acc0 = fadd2(acc0, make_float2(e0, e1));
     acc1 = fadd2(acc1, make_float2(e2, e3));
   }
-  float sum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
-  if (CELL == kI8) sum *= 0.0022326917f;   // 2^-8.807
-  if (CELL == kNv) sum *= 0.16666667f;     // 1/6
+  const float sum = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * sum_scale;
   st.d = st.d * alpha + sum;               // partial denominator of this half row
   st.m = m_new;
 
@@ -352,13 +371,21 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     // O may only be touched once the previous PV is complete.  The single FP16 P
     // buffer also needs that; the double-buffered 4/8-bit P tiles are free as soon as
     // this stage's scores arrived (QK of stage g is issued after PV of stage g-2).
-    if (need || CELL == kF16) {
-      wait(b, &b->o_done, (g - 1) & 1, p.status, 20 + CELL);
+    if (need || cell == kF16) {
+      // the previous stage's PV signals the release of its key/value slot
+      wait(b, prev_pv_bar, prev_pv_parity, p.status, 20 + cell);
       tc_fence_after_sync();
     }
     if (need) rescale_o<D>(tmem_row, half * (D / 2), alpha, phase_first ? colf : nullptr);
   }
-  write_p<CELL>(p_smem + p_buffer(CELL, g) * p_tile_bytes(CELL), row, half, s);
+  uint8_t* p_tile = p_smem + p_buffer(cell, g) * p_tile_bytes(cell);
+  if (cell == kNv) {
+    write_p<kNv>(p_tile, row, half, s);
+  } else if (cell == kI8) {
+    write_p<kI8>(p_tile, row, half, s);
+  } else {
+    write_p<kF16>(p_tile, row, half, s);
+  }
   fence_proxy_async_smem();
   tc_fence_before_sync();
   mbar_arrive(&b->p_full[g & 1]);
@@ -368,21 +395,21 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
 // MMA side
 // ------------------------------------------------------------------------------------------
 template <int D>
-__device__ __forceinline__ void issue_qk(int cell, uint32_t tmem, uint32_t q_addr, uint32_t k_addr,
-                                         uint32_t kv_slot_addr, uint32_t issue) {
+__device__ __forceinline__ void issue_qk(int cell, uint32_t tmem_s, uint32_t tmem, uint32_t q_addr,
+                                         uint32_t k_addr, uint32_t kv_slot_addr, uint32_t issue) {
   if (cell == kF16) {
     constexpr uint32_t chunks = D / 8;
     const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 16; ++k)
-      mma_f16_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+      mma_f16_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
                  smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else if (cell == kI8) {
     constexpr uint32_t chunks = D / 16;
     const uint32_t idesc = instr_desc(kFmtS8, kFmtS8, kAccS32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 32; ++k)
-      mma_i8_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+      mma_i8_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else {
     constexpr uint32_t chunks = D / 32;
@@ -393,7 +420,7 @@ __device__ __forceinline__ void issue_qk(int cell, uint32_t tmem, uint32_t q_add
       tmem_cp_32x128b_warpx4(tmem + kColSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128), issue);
 #pragma unroll
     for (int k = 0; k < D / 64; ++k)
-      mma_nvf4_ss(tmem + kColS, smem_desc(q_addr + k * 256, 128, chunks * 128),
+      mma_nvf4_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
                   smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0,
                   tmem + kColSfaQ + 4 * k, tmem + kColSfbK + 4 * k, issue);
   }
@@ -470,11 +497,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     }
     mbar_init(&b->q_full, 1);
     mbar_init(&b->q_free, 1);
-    mbar_init(&b->s_full, 1);
-    mbar_init(&b->s_free, kSoftmaxThreads);
+    mbar_init(&b->s_full[0], 1);
+    mbar_init(&b->s_full[1], 1);
+    mbar_init(&b->s_free[0], kSoftmaxThreads);
+    mbar_init(&b->s_free[1], kSoftmaxThreads);
     mbar_init(&b->p_full[0], kSoftmaxThreads);
     mbar_init(&b->p_full[1], kSoftmaxThreads);
-    mbar_init(&b->o_done, 1);
     mbar_init(&b->all_done, 1);
     b->abort = 0;
     mbar_init_fence();
@@ -555,6 +583,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     const uint32_t lead = lane == 0;
     int g = 0, phase_ord = 0;
     uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
+    int s_use0 = 0, s_use1 = 0;  // QK launches into each score buffer so far
     const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
     for (int cell = 0; cell < 3; ++cell) {
       if (cnt[cell] == 0) continue;
@@ -578,11 +607,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           const int slot = i % nslot;
           wait<true>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
           usepar ^= 1u << slot;
-          if (gi > 0) wait<true>(b, &b->s_free, (gi - 1) & 1, p.status, 5);
+          const int sb = s_buffer(cell, gi);
+          const int s_used = sb ? s_use1 : s_use0;
+          if (s_used > 0) wait<true>(b, &b->s_free[sb], (s_used - 1) & 1, p.status, 5);
+          s_use0 += sb ? 0 : 1;
+          s_use1 += sb ? 1 : 0;
           tc_fence_after_sync();
           const uint32_t slot_addr = ring_addr + slot * slot_bytes;
-          issue_qk<D>(cell, tmem, q_addr, slot_addr, slot_addr, lead);
-          mma_commit(&b->s_full, lead);
+          issue_qk<D>(cell, tmem + s_column(sb), tmem, q_addr, slot_addr, slot_addr, lead);
+          mma_commit(&b->s_full[sb], lead);
           if (i == n - 1) mma_commit(&b->q_free, lead);
         }
         if (i > 0) {
@@ -593,15 +626,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           const uint32_t slot_addr = ring_addr + slot * slot_bytes;
           issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
                       gj > 0, lead);
-          mma_commit(&b->o_done, lead);
-          mma_commit(&b->kv_free[slot], lead);
+          mma_commit(&b->kv_free[slot], lead);  // also tells the softmax warps this PV is done
         }
       }
       g += n;
       ++phase_ord;
     }
-    // A softmax warp that skipped o_done waits may be two phases behind on that barrier,
-    // so the end of the tile is signalled on a barrier of its own.
+    // The end of the tile is signalled on a barrier of its own.
     mma_commit(&b->all_done, lead);
   } else {
     // =============================== softmax rows ===============================
@@ -609,6 +640,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     const int row = (warp & 3) * 32 + lane;      // query row == TMEM lane
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     RowState st{-5.0e6f, 0.0f};
+    int s_use0 = 0, s_use1 = 0;  // stages consumed from each score buffer so far
+    uint32_t pvpar = 0;         // per slot: parity of the number of PVs that used it
+    int prev_slot = 0;
+    uint32_t prev_slot_parity = 0;
     int g = 0;
     int prev_cell = -1;
     const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
@@ -641,6 +676,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       // loads sit on the per-stage critical path.
       int meta_valid = 64;
       float meta_scale = 1.0f;
+      const int nslot = min(kMaxSlots, p.ring_bytes / ((CellInfo<D>::kv_bytes(cell) + 127) & ~127));
       const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
       for (int i = 0; i < cnt[cell]; ++i, ++g) {
         if ((i & 31) == 0) {
@@ -653,17 +689,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         }
         const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
         const bool phase_first = i == 0 && prev_cell >= 0;
-        if (cell == kNv) {
-          softmax_stage<kNv, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, base_scale,
-                                     valid, live_warp, st);
-        } else if (cell == kI8) {
-          const float sc = sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31));
-          softmax_stage<kI8, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first, sc, valid,
-                                     live_warp, st);
-        } else {
-          softmax_stage<kF16, D>(b, p, p_smem, colf, tmem_row, row, half, g, phase_first,
-                                      base_scale, valid, live_warp, st);
-        }
+        const int sb = s_buffer(cell, g);
+        const uint32_t s_parity = (sb ? s_use1 : s_use0) & 1;
+        s_use0 += sb ? 0 : 1;
+        s_use1 += sb ? 1 : 0;
+        // barrier that the PV of the previous stage completes (its key/value slot release)
+        uint64_t* pv_bar = &b->kv_free[prev_slot];
+        const uint32_t pv_parity = prev_slot_parity;
+        const int slot = i % nslot;
+        prev_slot = slot;
+        prev_slot_parity = (pvpar >> slot) & 1u;
+        pvpar ^= 1u << slot;
+        const float sc = cell == kI8
+                             ? sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31))
+                             : base_scale;
+        softmax_stage<D>(b, p, p_smem, colf, tmem_row, row, half, cell, g, phase_first, sc, valid,
+                         live_warp, sb, s_parity, pv_bar, pv_parity, st);
       }
       prev_cell = cell;
     }
@@ -734,9 +775,10 @@ int launch(AttnParams& p, int tiles, cudaStream_t st) {
   }
   (void)QB;
   q_region = (q_region + 1023) & ~1023;
-  const int fixed = q_region + p_region + D * 4 + (int)sizeof(Barriers) + 128;
-  const int budget = 113 * 1024;  // two CTAs per SM
-  int ring = ((budget - fixed) / 1024) * 1024;
+  const int fixed = q_region + p_region + D * 4 + (int)sizeof(Barriers);
+  // two CTAs per SM: measured limit is 115,528 bytes of dynamic shared memory per CTA
+  const int budget = 115528;
+  int ring = ((budget - fixed) / 128) * 128;
   ring = max(ring, 2 * ((slot + 127) & ~127));
   ring = min(ring, kMaxSlots * ((slot + 127) & ~127));
   p.ring_bytes = ring;

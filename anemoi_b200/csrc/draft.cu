@@ -22,8 +22,11 @@
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kChunk = 64;
-constexpr int kMaxBlocks = 4096;  // rows per head the shared-memory row buffers are sized for
+constexpr int kRowsPerWarp = 2;
+constexpr int kRows = kWarps * kRowsPerWarp;  // query blocks per CTA
+constexpr int kChunk = 128;                   // key blocks per pass: 4 per lane
+constexpr int kPitch = kChunk + 4;            // floats per channel row of the key tile
+constexpr int kMaxBlocks = 4096;              // rows per head the shared-memory buffers allow
 
 __device__ __forceinline__ float exp_canonical(float t) {
   const float y = fmaxf(__fmul_rn(t, __int_as_float(0x3fb8aa3b)), -125.0f);
@@ -40,44 +43,60 @@ __device__ __forceinline__ float exp_canonical(float t) {
   return __fmul_rn(p, __int_as_float((static_cast<int>(n) + 127) << 23));
 }
 
+// fp16 logits of kRows query blocks against every key block of the head.  Each warp owns
+// two rows, each lane four key columns of the 128-column pass: per channel one 16-byte
+// load of keys and one 8-byte load of the two query values feed eight FMAs.  Every logit
+// is still the plain channel-ordered FMA chain (the canonical order).
 template <int D>
 __device__ __forceinline__ void row_logits(const __half* q_pool, const __half* k_pool, int head,
-                                           int R, int row0, __half* kc, float* qs, __half* lg,
+                                           int R, int row0, float* kc, float* qs, __half* lg,
                                            int lg_stride) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = row0 + warp;
   const float scale = D == 64 ? 0.125f : __int_as_float(0x3db504f3);
-  // stage this CTA's query pools as floats
-  for (int idx = threadIdx.x; idx < kWarps * D; idx += kWarps * 32) {
-    const int r = row0 + idx / D;
-    qs[idx] = r < R ? __half2float(q_pool[((int64_t)head * R + r) * D + idx % D]) : 0.0f;
+  // query pools as floats, the two rows of a warp interleaved: qs[warp][channel][2]
+  for (int idx = threadIdx.x; idx < kRows * D; idx += kWarps * 32) {
+    const int r = idx / D, c = idx % D;
+    const int row = row0 + r;
+    qs[((r >> 1) * D + c) * 2 + (r & 1)] =
+        row < R ? __half2float(q_pool[((int64_t)head * R + row) * D + c]) : 0.0f;
   }
   for (int c0 = 0; c0 < R; c0 += kChunk) {
     __syncthreads();
-    // key pools of columns [c0, c0 + kChunk) transposed to [channel][column]
+    // key pools of columns [c0, c0 + kChunk) transposed to [channel][column] floats
     for (int idx = threadIdx.x; idx < kChunk * (D / 8); idx += kWarps * 32) {
-      const int col = idx / (D / 8), c8 = idx % (D / 8);
+      const int col = idx % kChunk, c8 = idx / kChunk;
       uint4 raw = make_uint4(0, 0, 0, 0);
       if (c0 + col < R)
         raw = __ldg(reinterpret_cast<const uint4*>(k_pool + ((int64_t)head * R + c0 + col) * D) + c8);
       const __half* h = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) kc[(c8 * 8 + i) * kChunk + col] = h[i];
+      for (int i = 0; i < 8; ++i) kc[(c8 * 8 + i) * kPitch + col] = __half2float(h[i]);
     }
     __syncthreads();
-    float acc0 = 0.0f, acc1 = 0.0f;
-    const float* qrow = qs + warp * D;
-#pragma unroll 8
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const float* qw = qs + warp * D * 2;
+#pragma unroll 4
     for (int c = 0; c < D; ++c) {
-      const float qv = qrow[c];
-      acc0 = __fmaf_rn(qv, __half2float(kc[c * kChunk + lane]), acc0);
-      acc1 = __fmaf_rn(qv, __half2float(kc[c * kChunk + lane + 32]), acc1);
+      const float2 qv = *reinterpret_cast<const float2*>(qw + c * 2);
+      const float4 kv = *reinterpret_cast<const float4*>(kc + c * kPitch + lane * 4);
+      acc[0][0] = __fmaf_rn(qv.x, kv.x, acc[0][0]);
+      acc[0][1] = __fmaf_rn(qv.x, kv.y, acc[0][1]);
+      acc[0][2] = __fmaf_rn(qv.x, kv.z, acc[0][2]);
+      acc[0][3] = __fmaf_rn(qv.x, kv.w, acc[0][3]);
+      acc[1][0] = __fmaf_rn(qv.y, kv.x, acc[1][0]);
+      acc[1][1] = __fmaf_rn(qv.y, kv.y, acc[1][1]);
+      acc[1][2] = __fmaf_rn(qv.y, kv.z, acc[1][2]);
+      acc[1][3] = __fmaf_rn(qv.y, kv.w, acc[1][3]);
     }
-    if (c0 + lane < R) lg[warp * lg_stride + c0 + lane] = __float2half_rn(__fmul_rn(acc0, scale));
-    if (c0 + lane + 32 < R)
-      lg[warp * lg_stride + c0 + lane + 32] = __float2half_rn(__fmul_rn(acc1, scale));
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = c0 + lane * 4 + j;
+        if (col < R)
+          lg[(warp * 2 + r) * lg_stride + col] = __float2half_rn(__fmul_rn(acc[r][j], scale));
+      }
   }
-  (void)row;
   __syncwarp();
 }
 
@@ -103,36 +122,38 @@ __global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool
                                                             float w, int R, __half* prob) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int lg_stride = (R + 7) & ~7;
-  __half* kc = reinterpret_cast<__half*>(smem_raw);                 // [D][kChunk]
-  float* qs = reinterpret_cast<float*>(kc + D * kChunk);            // [kWarps][D]
-  __half* lg = reinterpret_cast<__half*>(qs + kWarps * D);          // [kWarps][lg_stride]
-  __half* lgx = lg + kWarps * lg_stride;                            // blend only
-  const int head = blockIdx.y, row0 = blockIdx.x * kWarps;
+  float* kc = reinterpret_cast<float*>(smem_raw);                   // [D][kPitch]
+  float* qs = kc + D * kPitch;                                      // [kWarps][D][2]
+  __half* lg = reinterpret_cast<__half*>(qs + kRows * D);           // [kRows][lg_stride]
+  __half* lgx = lg + kRows * lg_stride;                             // blend only
+  const int head = blockIdx.y, row0 = blockIdx.x * kRows;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = row0 + warp;
 
   row_logits<D>(q_pool, k_pool, head, R, row0, kc, qs, lg, lg_stride);
   if (kBlend) {
     __syncthreads();
     row_logits<D>(q_max, k_max, head, R, row0, kc, qs, lgx, lg_stride);
   }
-  if (row >= R) return;
-  const __half* mine = lg + warp * lg_stride;
-  float m, inv;
-  row_stats(mine, R, m, inv);
-  __half* out = prob + ((int64_t)head * R + row) * R;
-  if (!kBlend) {
-    for (int j = lane; j < R; j += 32)
-      out[j] = __float2half_rn(__fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv));
-  } else {
-    const __half* minex = lgx + warp * lg_stride;
-    float mxx, invx;
-    row_stats(minex, R, mxx, invx);
-    const float wm = __fsub_rn(1.0f, w);
-    for (int j = lane; j < R; j += 32) {
-      const float pm = __fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv);
-      const float px = __fmul_rn(exp_canonical(__fsub_rn(__half2float(minex[j]), mxx)), invx);
-      out[j] = __float2half_rn(__fadd_rn(__fmul_rn(wm, pm), __fmul_rn(w, px)));
+  for (int r = 0; r < kRowsPerWarp; ++r) {
+    const int row = row0 + warp * 2 + r;
+    if (row >= R) break;
+    const __half* mine = lg + (warp * 2 + r) * lg_stride;
+    float m, inv;
+    row_stats(mine, R, m, inv);
+    __half* out = prob + ((int64_t)head * R + row) * R;
+    if (!kBlend) {
+      for (int j = lane; j < R; j += 32)
+        out[j] = __float2half_rn(__fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv));
+    } else {
+      const __half* minex = lgx + (warp * 2 + r) * lg_stride;
+      float mxx, invx;
+      row_stats(minex, R, mxx, invx);
+      const float wm = __fsub_rn(1.0f, w);
+      for (int j = lane; j < R; j += 32) {
+        const float pm = __fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv);
+        const float px = __fmul_rn(exp_canonical(__fsub_rn(__half2float(minex[j]), mxx)), invx);
+        out[j] = __float2half_rn(__fadd_rn(__fmul_rn(wm, pm), __fmul_rn(w, px)));
+      }
     }
   }
 }
@@ -141,13 +162,13 @@ template <int D, bool kBlend>
 int launch(const __half* qp, const __half* kp, const __half* qx, const __half* kx, float w, int R,
            int H, __half* prob, cudaStream_t st) {
   const int lg_stride = (R + 7) & ~7;
-  const size_t smem = (size_t)D * kChunk * 2 + (size_t)kWarps * D * 4 +
-                      (size_t)kWarps * lg_stride * 2 * (kBlend ? 2 : 1);
+  const size_t smem = (size_t)D * kPitch * 4 + (size_t)kRows * D * 4 +
+                      (size_t)kRows * lg_stride * 2 * (kBlend ? 2 : 1);
   auto kernel = draft_kernel<D, kBlend>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
-  dim3 grid((R + kWarps - 1) / kWarps, H);
+  dim3 grid((R + kRows - 1) / kRows, H);
   kernel<<<grid, kWarps * 32, smem, st>>>(qp, kp, qx, kx, w, R, prob);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
@@ -163,7 +184,8 @@ extern "C" int anemoi_sm100_draft_probability(const anemoi_sm100_shape* shape, c
   if (!(maxpool_weight >= 0.0f && maxpool_weight <= 1.0f)) return ANEMOI_SM100_EINVAL;
   if (maxpool_weight != 0.0f && (!q_max_pool || !k_max_pool)) return ANEMOI_SM100_EINVAL;
   const int R = shape->video_blocks, H = shape->heads, D = shape->head_dim;
-  if (R > kMaxBlocks) return ANEMOI_SM100_ELIMIT;
+  if (R > kMaxBlocks || (maxpool_weight != 0.0f && maxpool_weight != 1.0f && R > 2400))
+    return ANEMOI_SM100_ELIMIT;  // shared-memory row buffers
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __half* qp = static_cast<const __half*>(q_pool);
   const __half* kp = static_cast<const __half*>(k_pool);

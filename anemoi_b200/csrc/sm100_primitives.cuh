@@ -57,6 +57,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking test of the phase (never parks the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Same test, but lets the hardware park the thread for up to `hint_ns` before it reports
 // "not yet": fewer issue slots spent by threads that only wait (loader and MMA lanes).
 __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity,
