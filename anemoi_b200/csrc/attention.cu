@@ -128,6 +128,15 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return d;
 }
 
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -190,20 +199,22 @@ struct RowState {
   float m, d;
 };
 
-// O[row][c] *= alpha * colf[c] (colf may be null) for columns [c_begin, c_begin + D/2).
-template <int D>
+// O[row][c] *= alpha (* colf[c] when kColf) for columns [c_begin, c_begin + D/2).
+template <int D, bool kColf>
 __device__ __forceinline__ void rescale_o(uint32_t tmem_row, int c_begin, float alpha,
                                           const float* colf) {
+  const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll 1
   for (int c0 = c_begin; c0 < c_begin + D / 2; c0 += 32) {
     uint32_t r[32];
     tmem_ld32(tmem_row + kColO + c0, r);
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float v = __uint_as_float(r[j]) * alpha;
-      if (colf != nullptr) v *= colf[c0 + j];
-      r[j] = __float_as_uint(v);
+    for (int j = 0; j < 32; j += 2) {
+      float2 v = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), alpha2);
+      if (kColf) v = fmul2(v, *reinterpret_cast<const float2*>(colf + c0 + j));
+      r[j] = __float_as_uint(v.x);
+      r[j + 1] = __float_as_uint(v.y);
     }
     tmem_st32(tmem_row + kColO + c0, r);
   }
@@ -267,73 +278,107 @@ __device__ __forceinline__ int s_buffer(int cell, int g) { return cell == kNv ? 
 __device__ __forceinline__ uint32_t s_column(int sb) { return sb ? kColS1 : kColS; }
 
 // One stage of one phase for the thread's half row.  A single copy of this code serves the
-// three cells (the cell is a run-time argument and the function is not inlined): the kernel's
-// hot code has to stay well inside the instruction cache, and three unrolled copies did not.
+// three cells (the cell is a run-time value): the kernel's hot code has to stay well inside
+// the instruction cache, and three unrolled copies did not.
 template <int D>
-__device__ __noinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
-                                           const float* colf, uint32_t tmem_row, int row, int half,
-                                           int cell, int g, bool phase_first, float score_scale,
-                                           int valid, bool live_warp, int sb, uint32_t s_parity,
-                                           uint64_t* prev_pv_bar, uint32_t prev_pv_parity,
-                                           RowState& st) {
+__device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
+                                              const float* colf, uint32_t tmem_row, int row,
+                                              int half, int cell, int g, bool phase_first,
+                                              float score_scale, int valid, bool live_warp, int sb,
+                                              uint32_t s_parity, uint64_t* prev_pv_bar,
+                                              uint32_t prev_pv_parity, RowState& st) {
   wait(b, &b->s_full[sb], s_parity, p.status, 10 + cell);
   tc_fence_after_sync();
+  // Barrier arrivals are one per warp (lane 0 after a warp sync).
+  const bool lead = (row & 31) == 0;
   if (!live_warp) {
     // padding rows of a 64-row tile: keep the barrier protocol, skip the math
-    mbar_arrive(&b->s_free[sb]);
-    mbar_arrive(&b->p_full[g & 1]);
+    if (lead) {
+      mbar_arrive(&b->s_free[sb]);
+      mbar_arrive(&b->p_full[g & 1]);
+    }
     return;
   }
-  // INT8 cell: scores are s32; as_float(i + 0x4B400000) == 12582912 + i exactly for
-  // |i| < 2^22, a monotonic map, so the maximum is taken on those floats and 12582912 is
-  // subtracted afterwards (no integer->float conversion instruction).  The other cells add 0.
-  const int to_float = cell == kI8 ? 0x4B400000 : 0;
-  const float magic = cell == kI8 ? -12582912.0f : 0.0f;
-  // The row maximum needs all 64 scores: the other thread's 32 columns are loaded first,
-  // reduced to one value and dropped (TMEM reads are cheap; no exchange through shared
-  // memory), then the thread's own 32 columns.
+  // The row maximum needs all 64 scores: the partner thread's 32 columns are loaded first,
+  // reduced to one value and dropped (a TMEM read is cheaper than meeting the partner warp
+  // on a barrier), then the thread's own 32 columns.
   float s[32];
-  float mx;
+  float mx_other;
   {
-    const int mine = valid - 32 * half, theirs = valid - 32 * (half ^ 1);
-    float m0, m1;
-    {
-      uint32_t o[32];
-      tmem_ld32(tmem_row + s_column(sb) + 32 * (half ^ 1), o);
-      tmem_wait_ld();
-      float y[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) y[j] = __int_as_float((int)o[j] + to_float);
+    uint32_t o[32];
+    tmem_ld32(tmem_row + s_column(sb) + 32 * (half ^ 1), o);
+    tmem_wait_ld();
+    const int theirs = valid - 32 * (half ^ 1);
+    if (cell == kI8) {
+      // integer scores: maximum in the integer domain, one conversion
       if (theirs < 32) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = j < theirs ? y[j] : -INFINITY;
+        for (int j = 0; j < 32; ++j) o[j] = j < theirs ? o[j] : 0x80000000u;
       }
-      m0 = max3(y[0], y[1], y[2]);
-      m1 = max3(y[3], y[4], y[5]);
+      int m0 = max((int)o[0], (int)o[1]), m1 = max((int)o[2], (int)o[3]);
 #pragma unroll
-      for (int j = 6; j < 30; j += 4) {
-        m0 = max3(m0, y[j], y[j + 1]);
-        m1 = max3(m1, y[j + 2], y[j + 3]);
+      for (int j = 4; j < 32; j += 2) {
+        m0 = max(m0, (int)o[j]);
+        m1 = max(m1, (int)o[j + 1]);
       }
-      m0 = max3(m0, y[30], y[31]);
+      m0 = max(m0, m1);
+      mx_other = theirs > 0 ? (float)m0 : -INFINITY;
+    } else {
+      if (theirs < 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = j < theirs ? o[j] : 0xff800000u;
+      }
+      float m0 = max3(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]));
+      float m1 = max3(__uint_as_float(o[3]), __uint_as_float(o[4]), __uint_as_float(o[5]));
+#pragma unroll
+      for (int j = 6; j < 30; j += 6) {
+        m0 = max3(m0, __uint_as_float(o[j]), __uint_as_float(o[j + 1]));
+        m1 = max3(m1, __uint_as_float(o[j + 2]), __uint_as_float(o[j + 3]));
+        m0 = max3(m0, __uint_as_float(o[j + 4]), __uint_as_float(o[j + 5]));
+      }
+      mx_other = max3(m0, m1, fmaxf(__uint_as_float(o[30]), __uint_as_float(o[31])));
     }
+  }
+  {
     uint32_t r[32];
     tmem_ld32(tmem_row + s_column(sb) + 32 * half, r);
     tmem_wait_ld();
     tc_fence_before_sync();
-    mbar_arrive(&b->s_free[sb]);
+    __syncwarp();
+    if (lead) mbar_arrive(&b->s_free[sb]);
+    if (cell == kI8) {
+      // Scores are s32; as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, so
+      // the conversion is an integer add and a float subtract (no conversion instruction).
+      const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) s[j] = __int_as_float((int)r[j] + to_float);
-    if (mine < 32) {
+      for (int j = 0; j < 32; j += 2) {
+        const float2 v = fadd2(make_float2(__int_as_float((int)r[j] + 0x4B400000),
+                                           __int_as_float((int)r[j + 1] + 0x4B400000)),
+                               magic2);
+        s[j] = v.x;
+        s[j + 1] = v.y;
+      }
+    } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s[j] = j < mine ? s[j] : -INFINITY;
+      for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
     }
+  }
+  const int mine = valid - 32 * half;
+  if (mine < 32) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
+    for (int j = 0; j < 32; ++j) s[j] = j < mine ? s[j] : -INFINITY;
+  }
+  float mx;
+  {
+    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+#pragma unroll
+    for (int j = 6; j < 30; j += 6) {
       m0 = max3(m0, s[j], s[j + 1]);
       m1 = max3(m1, s[j + 2], s[j + 3]);
+      m0 = max3(m0, s[j + 4], s[j + 5]);
     }
-    mx = fmaxf(m0, m1) + magic;   // -inf stays -inf
+    m1 = max3(m1, s[30], s[31]);
+    mx = max3(m0, m1, mx_other);
   }
 
   const float m_new = fmaxf(st.m, mx * score_scale);
@@ -345,14 +390,11 @@ __device__ __noinline__ void softmax_stage(Barriers* b, const AttnParams& p, uin
   const float sum_scale = cell == kI8 ? 0.0022326917f : (cell == kNv ? 0.16666667f : 1.0f);
   const float2 scale2 = make_float2(score_scale, score_scale);
   const float2 bias2 = make_float2(bias, bias);
-  const float2 magic2 = make_float2(magic, magic);
   float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
-    float2 a0 = fadd2(make_float2(s[j], s[j + 1]), magic2);
-    float2 a1 = fadd2(make_float2(s[j + 2], s[j + 3]), magic2);
-    a0 = ffma2(a0, scale2, bias2);
-    a1 = ffma2(a1, scale2, bias2);
+    const float2 a0 = ffma2(make_float2(s[j], s[j + 1]), scale2, bias2);
+    const float2 a1 = ffma2(make_float2(s[j + 2], s[j + 3]), scale2, bias2);
     const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x);
     const float e3 = kPolyShare ? ex2_poly(a1.y) : ex2(a1.y);
     s[j] = e0;
@@ -376,7 +418,13 @@ __device__ __noinline__ void softmax_stage(Barriers* b, const AttnParams& p, uin
       wait(b, prev_pv_bar, prev_pv_parity, p.status, 20 + cell);
       tc_fence_after_sync();
     }
-    if (need) rescale_o<D>(tmem_row, half * (D / 2), alpha, phase_first ? colf : nullptr);
+    if (need) {
+      if (phase_first) {
+        rescale_o<D, true>(tmem_row, half * (D / 2), alpha, colf);
+      } else {
+        rescale_o<D, false>(tmem_row, half * (D / 2), alpha, nullptr);
+      }
+    }
   }
   uint8_t* p_tile = p_smem + p_buffer(cell, g) * p_tile_bytes(cell);
   if (cell == kNv) {
@@ -388,7 +436,8 @@ __device__ __noinline__ void softmax_stage(Barriers* b, const AttnParams& p, uin
   }
   fence_proxy_async_smem();
   tc_fence_before_sync();
-  mbar_arrive(&b->p_full[g & 1]);
+  __syncwarp();
+  if (lead) mbar_arrive(&b->p_full[g & 1]);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -499,10 +548,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     mbar_init(&b->q_free, 1);
     mbar_init(&b->s_full[0], 1);
     mbar_init(&b->s_full[1], 1);
-    mbar_init(&b->s_free[0], kSoftmaxThreads);
-    mbar_init(&b->s_free[1], kSoftmaxThreads);
-    mbar_init(&b->p_full[0], kSoftmaxThreads);
-    mbar_init(&b->p_full[1], kSoftmaxThreads);
+    mbar_init(&b->s_free[0], kSoftmaxThreads / 32);
+    mbar_init(&b->s_free[1], kSoftmaxThreads / 32);
+    mbar_init(&b->p_full[0], kSoftmaxThreads / 32);
+    mbar_init(&b->p_full[1], kSoftmaxThreads / 32);
     mbar_init(&b->all_done, 1);
     b->abort = 0;
     mbar_init_fence();
