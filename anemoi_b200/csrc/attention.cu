@@ -4,15 +4,14 @@
 // shape) and walks that tile's ragged list of 64-key stages in the order
 // NVFP4 -> INT8 -> FP16 with one online-softmax state.
 //
-// Warp roles (320 threads):
-//   warps 0-7  softmax: warps w and w+4 share TMEM lanes 32*(w%4).. (query rows); each
-//              thread owns half of its row's 64 scores (32 columns) and half of O's
-//              columns; the two threads of a row exchange their partial maximum through
-//              shared memory
-//   warp 8     loader: one lane issues 1-D bulk copies (TMA engine) of the Q record of
+// Warp roles (192 threads):
+//   warps 0-3  softmax: warp w owns TMEM lanes 32*w.. (query rows); one thread per row holds
+//              the row's 64 scores of a stage in registers (few threads with long unrolled
+//              instruction streams: the per-stage fixed cost is paid once per row)
+//   warp 4     loader: one lane issues 1-D bulk copies (TMA engine) of the Q record of
 //              each phase and of one K|V record per stage into a ring of shared-memory
 //              slots, completion counted on mbarriers
-//   warp 9     MMA: allocates TMEM; one lane issues tcgen05.mma
+//   warp 5     MMA: allocates TMEM; one lane issues tcgen05.mma
 //                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
 //                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
 //              and tcgen05.commit to mbarriers
@@ -49,10 +48,10 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreads = 320;
-constexpr int kSoftmaxThreads = 256;
-constexpr int kLoaderWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kLoaderWarp = 4;
+constexpr int kMmaWarp = 5;
 constexpr int kTmemCols = 256;
 constexpr int kColS = 0;
 constexpr int kColS1 = 192;  // second score buffer; aliases the scale-factor columns
@@ -199,13 +198,12 @@ struct RowState {
   float m, d;
 };
 
-// O[row][c] *= alpha (* colf[c] when kColf) for columns [c_begin, c_begin + D/2).
+// O[row][c] *= alpha (* colf[c] when kColf) for all D columns of the thread's row.
 template <int D, bool kColf>
-__device__ __forceinline__ void rescale_o(uint32_t tmem_row, int c_begin, float alpha,
-                                          const float* colf) {
+__device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const float* colf) {
   const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll 1
-  for (int c0 = c_begin; c0 < c_begin + D / 2; c0 += 32) {
+  for (int c0 = 0; c0 < D; c0 += 32) {
     uint32_t r[32];
     tmem_ld32(tmem_row + kColO + c0, r);
     tmem_wait_ld();
@@ -221,38 +219,41 @@ __device__ __forceinline__ void rescale_o(uint32_t tmem_row, int c_begin, float 
   tmem_wait_st();
 }
 
-// Writes the thread's 32 probabilities (keys 32*half .. 32*half+31 of its row) into the
-// K-major P tile in shared memory.
+// Writes the thread's 64 probabilities (one query row of the stage) into the K-major P tile
+// in shared memory.
 template <int CELL>
-__device__ __forceinline__ void write_p(uint8_t* p_tile, int row, int half, const float (&p)[32]) {
+__device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const float (&p)[64]) {
   if (CELL == kF16) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       uint4 v;
       __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j * 8 + 2 * i], p[j * 8 + 2 * i + 1]);
-      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half * 4 + j, 8)) = v;
+      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 8)) = v;
     }
   } else if (CELL == kI8) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < 4; ++j) {
       uint4 v;
       uint16_t* h = reinterpret_cast<uint16_t*>(&v);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         h[i] = __nv_cvt_float2_to_fp8x2(make_float2(p[j * 16 + 2 * i], p[j * 16 + 2 * i + 1]),
                                         __NV_SATFINITE, __NV_E4M3);
-      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half * 2 + j, 4)) = v;
+      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 4)) = v;
     }
   } else {
-    uint4 v;
-    uint8_t* h = reinterpret_cast<uint8_t*>(&v);
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-      h[i] = __nv_cvt_float2_to_fp4x2(make_float2(p[2 * i], p[2 * i + 1]), __NV_E2M1,
-                                      cudaRoundNearest);  // p already holds 6 P
-    *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, half, 2)) = v;
+    for (int j = 0; j < 2; ++j) {
+      uint4 v;
+      uint8_t* h = reinterpret_cast<uint8_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        h[i] = __nv_cvt_float2_to_fp4x2(make_float2(p[j * 32 + 2 * i], p[j * 32 + 2 * i + 1]),
+                                        __NV_E2M1, cudaRoundNearest);  // p already holds 6 P
+      *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 2)) = v;
+    }
   }
 }
 
@@ -277,13 +278,13 @@ __device__ __forceinline__ int p_buffer(int cell, int g) { return cell == kF16 ?
 __device__ __forceinline__ int s_buffer(int cell, int g) { return cell == kNv ? 0 : (g & 1); }
 __device__ __forceinline__ uint32_t s_column(int sb) { return sb ? kColS1 : kColS; }
 
-// One stage of one phase for the thread's half row.  A single copy of this code serves the
-// three cells (the cell is a run-time value): the kernel's hot code has to stay well inside
-// the instruction cache, and three unrolled copies did not.
+// One stage of one phase for the thread's row.  A single copy of this code serves the three
+// cells (the cell is a run-time value): the kernel's hot code has to stay well inside the
+// instruction cache, and three unrolled copies did not.
 template <int D>
 __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
                                               const float* colf, uint32_t tmem_row, int row,
-                                              int half, int cell, int g, bool phase_first,
+                                              int cell, int g, bool phase_first,
                                               float score_scale, int valid, bool live_warp, int sb,
                                               uint32_t s_parity, uint64_t* prev_pv_bar,
                                               uint32_t prev_pv_parity, RowState& st) {
@@ -299,49 +300,11 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     }
     return;
   }
-  // The row maximum needs all 64 scores: the partner thread's 32 columns are loaded first,
-  // reduced to one value and dropped (a TMEM read is cheaper than meeting the partner warp
-  // on a barrier), then the thread's own 32 columns.
-  float s[32];
-  float mx_other;
+  float s[64];
   {
-    uint32_t o[32];
-    tmem_ld32(tmem_row + s_column(sb) + 32 * (half ^ 1), o);
-    tmem_wait_ld();
-    const int theirs = valid - 32 * (half ^ 1);
-    if (cell == kI8) {
-      // integer scores: maximum in the integer domain, one conversion
-      if (theirs < 32) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = j < theirs ? o[j] : 0x80000000u;
-      }
-      int m0 = max((int)o[0], (int)o[1]), m1 = max((int)o[2], (int)o[3]);
-#pragma unroll
-      for (int j = 4; j < 32; j += 2) {
-        m0 = max(m0, (int)o[j]);
-        m1 = max(m1, (int)o[j + 1]);
-      }
-      m0 = max(m0, m1);
-      mx_other = theirs > 0 ? (float)m0 : -INFINITY;
-    } else {
-      if (theirs < 32) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = j < theirs ? o[j] : 0xff800000u;
-      }
-      float m0 = max3(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]));
-      float m1 = max3(__uint_as_float(o[3]), __uint_as_float(o[4]), __uint_as_float(o[5]));
-#pragma unroll
-      for (int j = 6; j < 30; j += 6) {
-        m0 = max3(m0, __uint_as_float(o[j]), __uint_as_float(o[j + 1]));
-        m1 = max3(m1, __uint_as_float(o[j + 2]), __uint_as_float(o[j + 3]));
-        m0 = max3(m0, __uint_as_float(o[j + 4]), __uint_as_float(o[j + 5]));
-      }
-      mx_other = max3(m0, m1, fmaxf(__uint_as_float(o[30]), __uint_as_float(o[31])));
-    }
-  }
-  {
-    uint32_t r[32];
-    tmem_ld32(tmem_row + s_column(sb) + 32 * half, r);
+    uint32_t r[64];
+    tmem_ld32(tmem_row + s_column(sb), *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_ld32(tmem_row + s_column(sb) + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
     tmem_wait_ld();
     tc_fence_before_sync();
     __syncwarp();
@@ -351,7 +314,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
       // the conversion is an integer add and a float subtract (no conversion instruction).
       const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
+      for (int j = 0; j < 64; j += 2) {
         const float2 v = fadd2(make_float2(__int_as_float((int)r[j] + 0x4B400000),
                                            __int_as_float((int)r[j + 1] + 0x4B400000)),
                                magic2);
@@ -360,31 +323,33 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(r[j]);
+      for (int j = 0; j < 64; ++j) s[j] = __uint_as_float(r[j]);
     }
   }
-  const int mine = valid - 32 * half;
-  if (mine < 32) {
+  if (valid < 64) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) s[j] = j < mine ? s[j] : -INFINITY;
+    for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
   }
   float mx;
   {
     float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-    for (int j = 6; j < 30; j += 6) {
+    for (int j = 12; j < 60; j += 8) {
       m0 = max3(m0, s[j], s[j + 1]);
       m1 = max3(m1, s[j + 2], s[j + 3]);
-      m0 = max3(m0, s[j + 4], s[j + 5]);
+      m2 = max3(m2, s[j + 4], s[j + 5]);
+      m3 = max3(m3, s[j + 6], s[j + 7]);
     }
-    m1 = max3(m1, s[30], s[31]);
-    mx = max3(m0, m1, mx_other);
+    m0 = max3(m0, s[60], s[61]);
+    m1 = max3(m1, s[62], s[63]);
+    mx = fmaxf(max3(m0, m1, m2), m3);
   }
 
   const float m_new = fmaxf(st.m, mx * score_scale);
   const float alpha = ex2(st.m - m_new);
   // exponent = s * scale + bias; the NVFP4 cell produces 6 P directly (e2m1 input range),
-  // the INT8 cell P * 2^8.807 (e4m3 input range); the partial sums are scaled back.
+  // the INT8 cell P * 2^8.807 (e4m3 input range); the sums are scaled back.
   const float bias = cell == kI8 ? kFp8Offset - m_new
                                  : (cell == kNv ? 2.5849625007f - m_new : -m_new);
   const float sum_scale = cell == kI8 ? 0.0022326917f : (cell == kNv ? 0.16666667f : 1.0f);
@@ -392,7 +357,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
   const float2 bias2 = make_float2(bias, bias);
   float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
+  for (int j = 0; j < 64; j += 4) {
     const float2 a0 = ffma2(make_float2(s[j], s[j + 1]), scale2, bias2);
     const float2 a1 = ffma2(make_float2(s[j + 2], s[j + 3]), scale2, bias2);
     const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x);
@@ -405,7 +370,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     acc1 = fadd2(acc1, make_float2(e2, e3));
   }
   const float sum = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * sum_scale;
-  st.d = st.d * alpha + sum;               // partial denominator of this half row
+  st.d = st.d * alpha + sum;
   st.m = m_new;
 
   if (g > 0) {
@@ -420,19 +385,19 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     }
     if (need) {
       if (phase_first) {
-        rescale_o<D, true>(tmem_row, half * (D / 2), alpha, colf);
+        rescale_o<D, true>(tmem_row, alpha, colf);
       } else {
-        rescale_o<D, false>(tmem_row, half * (D / 2), alpha, nullptr);
+        rescale_o<D, false>(tmem_row, alpha, nullptr);
       }
     }
   }
   uint8_t* p_tile = p_smem + p_buffer(cell, g) * p_tile_bytes(cell);
   if (cell == kNv) {
-    write_p<kNv>(p_tile, row, half, s);
+    write_p<kNv>(p_tile, row, s);
   } else if (cell == kI8) {
-    write_p<kI8>(p_tile, row, half, s);
+    write_p<kI8>(p_tile, row, s);
   } else {
-    write_p<kF16>(p_tile, row, half, s);
+    write_p<kF16>(p_tile, row, s);
   }
   fence_proxy_async_smem();
   tc_fence_before_sync();
@@ -610,11 +575,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         if ((filled >> sl) & 1u)
           wait<true>(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
       int stage_l = 0;  // list entries, 32 at a time, one per lane
+      int slot = -1;
       for (int i = 0; i < cnt[cell]; ++i) {
         if ((i & 31) == 0 && list != nullptr && i + lane < cnt[cell])
           stage_l = list[first + i + lane];
         const int stage = list ? __shfl_sync(0xffffffffu, stage_l, i & 31) : i;
-        const int slot = i % nslot;
+        slot = slot + 1 == nslot ? 0 : slot + 1;
         if ((filled >> slot) & 1u)
           wait<true>(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
         mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes, lead);
@@ -650,10 +616,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
       const uint32_t ring_addr = smem_u32(slots);
       // software pipeline: QK of stage i+1 is issued before PV of stage i
+      int qk_slot = 0, pv_slot = 0;
       for (int i = 0; i <= n; ++i) {
         if (i < n) {
           const int gi = g + i;
-          const int slot = i % nslot;
+          const int slot = qk_slot;
+          qk_slot = qk_slot + 1 == nslot ? 0 : qk_slot + 1;
           wait<true>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
           usepar ^= 1u << slot;
           const int sb = s_buffer(cell, gi);
@@ -669,7 +637,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         }
         if (i > 0) {
           const int gj = g + i - 1;
-          const int slot = (i - 1) % nslot;
+          const int slot = pv_slot;
+          pv_slot = pv_slot + 1 == nslot ? 0 : pv_slot + 1;
           wait<true>(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
           tc_fence_after_sync();
           const uint32_t slot_addr = ring_addr + slot * slot_bytes;
@@ -685,9 +654,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     mma_commit(&b->all_done, lead);
   } else {
     // =============================== softmax rows ===============================
-    const int half = warp >> 2;                  // which 32 score columns / D/2 output columns
-    const int row = (warp & 3) * 32 + lane;      // query row == TMEM lane
-    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int row = warp * 32 + lane;            // query row == TMEM lane
+    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
     RowState st{-5.0e6f, 0.0f};
     int s_use0 = 0, s_use1 = 0;  // stages consumed from each score buffer so far
     uint32_t pvpar = 0;         // per slot: parity of the number of PVs that used it
@@ -697,7 +665,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     int prev_cell = -1;
     const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
     const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
-    const bool live_warp = (warp & 3) * 32 < QB;
+    const bool live_warp = warp * 32 < QB;
     if (cnt[kNv] > 0) {
       tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
       tmem_wait_st();
@@ -706,14 +674,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       if (cnt[cell] == 0) continue;
       if (prev_cell >= 0) {
         // per-channel factor that moves O from the previous phase's domain into this one's
-        asm volatile("bar.sync 5, 256;" ::: "memory");
+        asm volatile("bar.sync 5, 128;" ::: "memory");
         for (int c = threadIdx.x; c < D; c += kSoftmaxThreads) {
           const float from = prev_cell == kNv ? nv_dom
                                               : (prev_cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f);
           const float to = cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f;
           colf[c] = to == 0.0f ? 0.0f : from / to;
         }
-        asm volatile("bar.sync 5, 256;" ::: "memory");
+        asm volatile("bar.sync 5, 128;" ::: "memory");
       }
       const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
       const float q_scale =
@@ -727,13 +695,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       float meta_scale = 1.0f;
       const int nslot = min(kMaxSlots, p.ring_bytes / ((CellInfo<D>::kv_bytes(cell) + 127) & ~127));
       const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
+      int slot = 0;
       for (int i = 0; i < cnt[cell]; ++i, ++g) {
         if ((i & 31) == 0) {
           const int mine = i + lane;
           if (mine < cnt[cell]) {
             const int stage = list ? list[first + mine] : mine;
             meta_valid = p.valid_k[stage];
-            if (cell == kI8) meta_scale = kscale[stage];
+            if (cell == kI8) meta_scale = sigma * (q_scale * kscale[stage]);
           }
         }
         const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
@@ -745,14 +714,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         // barrier that the PV of the previous stage completes (its key/value slot release)
         uint64_t* pv_bar = &b->kv_free[prev_slot];
         const uint32_t pv_parity = prev_slot_parity;
-        const int slot = i % nslot;
         prev_slot = slot;
         prev_slot_parity = (pvpar >> slot) & 1u;
         pvpar ^= 1u << slot;
-        const float sc = cell == kI8
-                             ? sigma * (q_scale * __shfl_sync(0xffffffffu, meta_scale, i & 31))
-                             : base_scale;
-        softmax_stage<D>(b, p, p_smem, colf, tmem_row, row, half, cell, g, phase_first, sc, valid,
+        slot = slot + 1 == nslot ? 0 : slot + 1;
+        const float sc =
+            cell == kI8 ? __shfl_sync(0xffffffffu, meta_scale, i & 31) : base_scale;
+        softmax_stage<D>(b, p, p_smem, colf, tmem_row, row, cell, g, phase_first, sc, valid,
                          live_warp, sb, s_parity, pv_bar, pv_parity, st);
       }
       prev_cell = cell;
@@ -761,15 +729,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     wait(b, &b->all_done, 0, p.status, 7);
     if (live_warp) {
       tc_fence_after_sync();
-      // partial denominators of the two half rows meet in the (now idle) P tile
-      float* xsum = reinterpret_cast<float*>(p_smem);
-      xsum[half * 128 + row] = st.d;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + (row >> 5)) : "memory");
-      const float inv = 1.0f / (st.d + xsum[(half ^ 1) * 128 + row]);
+      const float inv = 1.0f / st.d;
       const bool live = row < QB;
       __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)tile * QB + row) * D;
 #pragma unroll 1
-      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_row + kColO + c0, r);
         tmem_wait_ld();
