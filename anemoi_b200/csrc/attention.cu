@@ -151,14 +151,15 @@ template <bool kPark>
 __device__ __noinline__ void wait_slow(Barriers* b, uint64_t* bar, uint32_t parity,
                                        int32_t* status, int where) {
   uint64_t t0 = 0;
-  for (uint32_t spin = 0;; ++spin) {
-    if (kPark ? mbar_try_wait_hint(bar, parity, 4000u) : mbar_try_wait(bar, parity)) return;
+  for (;;) {
+    // tight inner polls; the abort flag and the clock are looked at once per batch
+#pragma unroll 1
+    for (int k = 0; k < (kPark ? 16 : 256); ++k)
+      if (kPark ? mbar_try_wait_hint(bar, parity, 4000u) : mbar_try_wait(bar, parity)) return;
     if (b->abort) return;
-    if ((spin & (kPark ? 63u : 1023u)) == (kPark ? 63u : 1023u)) {
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > 2000000000ull) break;
-    }
+    const uint64_t now = globaltimer_ns();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > 2000000000ull) break;
   }
   b->abort = 1;
   atomicCAS(status, 0, where);
@@ -327,8 +328,14 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     }
   }
   if (valid < 64) {
+    // ragged blocks usually lose only a few keys: the common case touches the last 8 columns
+    if (valid >= 56) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+      for (int j = 56; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+    }
   }
   float mx;
   {
