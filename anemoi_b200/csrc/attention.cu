@@ -62,7 +62,6 @@ constexpr int kColSfaP = 208;
 constexpr int kColSfbV = 212;
 constexpr int kMaxSlots = 8;
 constexpr float kFp8Offset = 8.807f;
-constexpr bool kPolyShare = false;  // true: every 4th probability uses ex2_poly
 
 enum Cell : int { kNv = 0, kI8 = 1, kF16 = 2 };
 
@@ -147,15 +146,19 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // abort flag.  It returns nothing: after an abort every later wait falls through, so each
 // role runs its loops to the end with uniform control flow and the CTA exits normally (its
 // output is invalid, which the status word tells the host).
-template <bool kPark>
+// kSleepNs > 0 (loader and MMA warps, which wait most of the time): sleep between polls, so
+// that their polling does not take issue slots from the softmax warps of the same scheduler.
+template <int kSleepNs>
 __device__ __noinline__ void wait_slow(Barriers* b, uint64_t* bar, uint32_t parity,
                                        int32_t* status, int where) {
   uint64_t t0 = 0;
   for (;;) {
     // tight inner polls; the abort flag and the clock are looked at once per batch
 #pragma unroll 1
-    for (int k = 0; k < (kPark ? 16 : 256); ++k)
-      if (kPark ? mbar_try_wait_hint(bar, parity, 4000u) : mbar_try_wait(bar, parity)) return;
+    for (int k = 0; k < (kSleepNs > 0 ? 64 : 256); ++k) {
+      if (mbar_try_wait(bar, parity)) return;
+      if (kSleepNs > 0) asm volatile("nanosleep.u32 %0;" ::"n"(kSleepNs));
+    }
     if (b->abort) return;
     const uint64_t now = globaltimer_ns();
     if (t0 == 0) t0 = now;
@@ -166,11 +169,11 @@ __device__ __noinline__ void wait_slow(Barriers* b, uint64_t* bar, uint32_t pari
 }
 
 // One inline poll; the bounded spin loop is a shared out-of-line function (code size).
-template <bool kPark = false>
+template <int kSleepNs = 0>
 __device__ __forceinline__ void wait(Barriers* b, uint64_t* bar, uint32_t parity, int32_t* status,
                                      int where) {
   if (mbar_try_wait(bar, parity)) return;
-  wait_slow<kPark>(b, bar, parity, status, where);
+  wait_slow<kSleepNs>(b, bar, parity, status, where);
 }
 
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t v) {
@@ -256,18 +259,6 @@ __device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const float (&
       *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 2)) = v;
     }
   }
-}
-
-// 2^x on the FMA/ALU pipes (Cody-Waite split + degree-3 polynomial, relative error ~1e-4),
-// used for a share of the probabilities so the MUFU unit is not the only exp engine.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float xr = x + 12582912.0f;             // 1.5 * 2^23: integer part lands in the low mantissa bits
-  const float f = x - (xr - 12582912.0f);      // fractional part in [-0.5, 0.5]
-  float p = fmaf(f, 0.05550410866f, 0.2402265069f);
-  p = fmaf(p, f, 0.6931471806f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
 }
 
 // Bytes of one P tile (128 rows x 64 keys) per cell, and which of the two buffers stage g uses.
@@ -367,8 +358,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
   for (int j = 0; j < 64; j += 4) {
     const float2 a0 = ffma2(make_float2(s[j], s[j + 1]), scale2, bias2);
     const float2 a1 = ffma2(make_float2(s[j + 2], s[j + 3]), scale2, bias2);
-    const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x);
-    const float e3 = kPolyShare ? ex2_poly(a1.y) : ex2(a1.y);
+    const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x), e3 = ex2(a1.y);
     s[j] = e0;
     s[j + 1] = e1;
     s[j + 2] = e2;
@@ -552,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     uint32_t filled = 0, fillpar = 0;  // per slot: ever filled / parity of the fill count
     for (int cell = 0; cell < 3; ++cell) {
       if (cnt[cell] == 0) continue;
-      if (phase_ord > 0) wait<true>(b, &b->q_free, (phase_ord - 1) & 1, p.status, 1);
+      if (phase_ord > 0) wait<400>(b, &b->q_free, (phase_ord - 1) & 1, p.status, 1);
       const int qbytes = CellInfo<D>::q_bytes(cell, QB);
       const uint8_t* qsrc =
           cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
@@ -580,7 +570,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
       for (int sl = 0; sl < kMaxSlots; ++sl)
         if ((filled >> sl) & 1u)
-          wait<true>(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
+          wait<400>(b, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, p.status, 2);
       int stage_l = 0;  // list entries, 32 at a time, one per lane
       int slot = -1;
       for (int i = 0; i < cnt[cell]; ++i) {
@@ -589,7 +579,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         const int stage = list ? __shfl_sync(0xffffffffu, stage_l, i & 31) : i;
         slot = slot + 1 == nslot ? 0 : slot + 1;
         if ((filled >> slot) & 1u)
-          wait<true>(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
+          wait<400>(b, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, p.status, 2);
         mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes, lead);
         bulk_g2s(slots + (size_t)slot * slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
                  &b->kv_full[slot], lead);
@@ -609,7 +599,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
     for (int cell = 0; cell < 3; ++cell) {
       if (cnt[cell] == 0) continue;
-      wait<true>(b, &b->q_full, phase_ord & 1, p.status, 3);
+      wait<200>(b, &b->q_full, phase_ord & 1, p.status, 3);
       tc_fence_after_sync();
       if (cell == kNv) {
         const uint32_t qsf = q_addr + 128 * D / 2;
@@ -629,11 +619,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           const int gi = g + i;
           const int slot = qk_slot;
           qk_slot = qk_slot + 1 == nslot ? 0 : qk_slot + 1;
-          wait<true>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
+          wait<50>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
           usepar ^= 1u << slot;
           const int sb = s_buffer(cell, gi);
           const int s_used = sb ? s_use1 : s_use0;
-          if (s_used > 0) wait<true>(b, &b->s_free[sb], (s_used - 1) & 1, p.status, 5);
+          if (s_used > 0) wait<50>(b, &b->s_free[sb], (s_used - 1) & 1, p.status, 5);
           s_use0 += sb ? 0 : 1;
           s_use1 += sb ? 1 : 0;
           tc_fence_after_sync();
@@ -646,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           const int gj = g + i - 1;
           const int slot = pv_slot;
           pv_slot = pv_slot + 1 == nslot ? 0 : pv_slot + 1;
-          wait<true>(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
+          wait<100>(b, &b->p_full[gj & 1], (gj >> 1) & 1, p.status, 6);
           tc_fence_after_sync();
           const uint32_t slot_addr = ring_addr + slot * slot_bytes;
           issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
