@@ -237,6 +237,34 @@ def workload_config(n_gpus: int) -> dict:
             "l2": "inputs (3.66 GB of Q/K/V) exceed the 126 MB L2; no explicit flush"}
 
 
+def dense_flash_sample(q, k, v, heads: int = 8) -> dict:
+    """Dense bf16 attention of the same sequence through torch's library kernel, for context.
+
+    Timed on `heads` heads (the cost is linear in heads) and scaled to all of them.  It is a
+    comparison figure only: nothing of the sparse layer runs through it.
+    """
+    import torch.nn.functional as F
+
+    h_all = q.shape[2]
+    heads = min(heads, h_all)
+    qq, kk, vv = (x[:, :, :heads].transpose(1, 2).contiguous() for x in (q, k, v))
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    try:
+        F.scaled_dot_product_attention(qq, kk, vv)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(2):
+            F.scaled_dot_product_attention(qq, kk, vv)
+        end.record()
+        torch.cuda.synchronize()
+    except RuntimeError as exc:  # out of memory or no kernel for this shape
+        return {"unavailable": str(exc).splitlines()[0][:120]}
+    ms = start.elapsed_time(end) / 2 * (h_all / heads)
+    s_total, d = q.shape[1], q.shape[3]
+    return {"ms_per_layer": ms, "tflops": dense_equivalent_flops(s_total, d, h_all) / (ms * 1e-3) / 1e12,
+            "impl": f"torch scaled_dot_product_attention (library kernel), {heads} of {h_all} heads timed, scaled"}
+
+
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
@@ -361,6 +389,11 @@ def run_ours(args) -> None:
         mixed_peak = (f4 + f8 + f16) / (f4 / (4 * bf16) + f8 / (2 * bf16) + f16 / bf16)
         attn_ms = stages.get("attention", float("nan"))
         achieved = video_flops / (attn_ms * 1e-3) / 1e12 if attn_ms == attn_ms else None
+        # DRAM traffic of one video-attention launch: the ncu capture of the small profiling case
+        # (profiles/attention_kernel_small_case.md: 304.5 MB read + 63.9 MB written for 8 heads of
+        # 33,272 tokens) scaled by heads x tokens; the operands of a head stay L2-resident in both
+        # cases, so the traffic is the compulsory read of the records and the write of O.
+        traffic = (304.453376e6 + 63.904768e6) / (8 * 33272) * heads_local * s_total
         line = {
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -376,10 +409,13 @@ def run_ours(args) -> None:
             "stage_ms": stages,
             "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
                          "achieved": achieved, "peak": mixed_peak, "unit": "TFLOP/s",
-                         "frac": (achieved / mixed_peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / mixed_peak) if achieved else None, "traffic": traffic,
+                         "traffic_source": "ncu dram bytes of the 8-head S=33,272 case, scaled by heads x tokens",
                          "peak_source": f"{peak_kind} bf16 GEMM {bf16} TFLOP/s x (1, 2, 4) for fp16, 8-bit, NVFP4 "
                                         "cells, weighted by executed FLOPs"},
         }
+        if world == 1 and not args.no_dense:
+            line["dense_bf16"] = dense_flash_sample(q, k, v)
         if world == 1 and not args.no_cpu_baseline:
             cpu = cpu_sample(w, query_blocks=3)
             line["cpu_baseline"] = {"value": cpu["tflops"], "unit": "TFLOP/s dense-equivalent",
@@ -397,6 +433,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dense", action="store_true",
+                    help="skip the dense bf16 library attention timed beside the sparse layer")
     ap.add_argument("--profile-case", action="store_true",
                     help="run the small profiling case instead of the benchmark workload")
     args = ap.parse_args()

@@ -154,6 +154,28 @@ def test_output_within_tolerance(run):
     assert not np.isnan(got).any()
 
 
+def test_error_versus_dense_attention_is_reported(run, record_property):
+    """Error of the sparse mixed-precision result against dense fp64 attention of the same
+    inputs: reported per case, and the GPU path must be as far from dense as the oracle is
+    (the sparsity and quantisation error belong to the algorithm, not to the implementation)."""
+    from oracle.attention import dense_reference
+
+    case, (out, parts, oracle, geo) = run
+    name, vs, prefix, H, D, QB, dtype, ratios, drop, w, pkv, pq = case
+    f, hh, ww = vs
+    outl = (17, 53) if D == 64 else (17, 93)
+    q, k, v = smooth_fields(f, hh, ww, H, D, prefix, seed=0, outliers=outl if dtype == torch.bfloat16 else (), dtype=dtype)
+    got = out[0].float().cpu().numpy()
+    h = 0
+    dense = dense_reference(q[0, :, h].float().numpy(), k[0, :, h].float().numpy(), v[0, :, h].float().numpy())
+    ma_g, cos_g, rel_g = compare_metrics(got[:, h], dense)
+    ma_o, cos_o, rel_o = compare_metrics(oracle[h][0].astype(np.float32), dense)
+    record_property("dense_error", {"case": name, "gpu": (ma_g, cos_g, rel_g), "oracle": (ma_o, cos_o, rel_o)})
+    print(f"[{name}] vs dense fp64: gpu max_abs={ma_g:.4f} cos={cos_g:.5f} rel={rel_g:.4f} | "
+          f"oracle max_abs={ma_o:.4f} cos={cos_o:.5f} rel={rel_o:.4f}")
+    assert abs(rel_g - rel_o) <= 5e-3 and abs(cos_g - cos_o) <= 1e-3
+
+
 def test_public_api_matches_executor(run):
     from anemoi_b200 import (NVFP4Calibration, QuantConfig, SparseConfig, VisualLayout,
                              anemoi_attention)
