@@ -83,6 +83,7 @@ def library() -> C.CDLL:
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
         "anemoi_sm100_pack_qkv": (C.c_int, [P, P, P, P, I64, I32, I32, I32, C.POINTER(I64), P]),
         "anemoi_sm100_merge_heads": (C.c_int, [P, P, I64, I32, I32, I32, P]),
+        "anemoi_sm100_tensor_peak": (C.c_int, [I32, I32, P, C.POINTER(C.c_double), P]),
     }
     for name, (restype, argtypes) in signatures.items():
         fn = getattr(lib, name)
@@ -99,7 +100,7 @@ EXPORTED = (
     "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
-    "anemoi_sm100_merge_heads",
+    "anemoi_sm100_merge_heads", "anemoi_sm100_tensor_peak",
 )
 
 
@@ -303,3 +304,34 @@ def merge_heads(x: torch.Tensor) -> torch.Tensor:
     _check(library().anemoi_sm100_merge_heads(_ptr(x), _ptr(out), rows, world, hl, d,
                                               _stream(x.device)), "anemoi_sm100_merge_heads")
     return out
+
+
+TENSOR_KINDS = {"f16": 0, "i8": 1, "f8": 2, "nvfp4": 3}
+
+
+def tensor_peak(kind: str, device=None, iterations: int = 4096, repeats: int = 3) -> float:
+    """Measured tcgen05 throughput (TFLOP/s, or TOP/s for ``i8``) of one MMA kind.
+
+    Runs the library's tensor-pipe probe (128x128 tiles, operands in shared memory, two CTAs per
+    SM) ``repeats`` times after one warm-up and returns the best rate.  Measurement helper for
+    the roofline denominators; it has no part in the attention path.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    lib = library()
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    flops = C.c_double(0.0)
+    best = 0.0
+    with torch.cuda.device(device):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for rep in range(repeats + 1):
+            start.record()
+            _check(lib.anemoi_sm100_tensor_peak(TENSOR_KINDS[kind], iterations, _ptr(status),
+                                                C.byref(flops), _stream(device)),
+                   "anemoi_sm100_tensor_peak")
+            end.record()
+            end.synchronize()
+            if rep > 0:
+                best = max(best, flops.value / (start.elapsed_time(end) * 1e-3) / 1e12)
+    if int(status.item()) != 0:
+        raise RuntimeError("anemoi_sm100_tensor_peak: a bounded wait gave up")
+    return best

@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[2], the configuration the metric is quoted on):
+Workload (the third benchmark configuration, the one the metric is quoted on):
 512-token prefix + 21x48x84 video tokens (S = 85,184), 56 heads, D = 128, bf16,
 Q128 query blocks, 80 % of block pairs dropped, retained pairs split NVFP4 / INT8 /
 FP16 = 40 / 40 / 20, NVFP4 global scales amax/(6*448).  Inputs are seeded synthetic
@@ -230,7 +230,7 @@ def run_reference(args) -> None:
 
 def workload_config(n_gpus: int) -> dict:
     w = WORKLOAD
-    return {"workload": "BASELINE configs[2]: prefix 512 + video 21x48x84 (S=85184), H=56, D=128, bf16, "
+    return {"workload": "configs[2]: prefix 512 + video 21x48x84 (S=85184), H=56, D=128, bf16, "
                         "Q128, 80% block drop, NVFP4/INT8/FP16 = 40/40/20, prefix K/V and prefix queries INT8",
             "parallelism": f"ulysses{n_gpus}" if n_gpus > 1 else "single",
             "heads_per_gpu": w["heads"] // n_gpus,
@@ -390,8 +390,8 @@ def run_ours(args) -> None:
         attn_ms = stages.get("attention", float("nan"))
         achieved = video_flops / (attn_ms * 1e-3) / 1e12 if attn_ms == attn_ms else None
         # DRAM traffic of one video-attention launch: the ncu capture of the small profiling case
-        # (profiles/attention_kernel_small_case.md: 304.5 MB read + 63.9 MB written for 8 heads of
-        # 33,272 tokens) scaled by heads x tokens; the operands of a head stay L2-resident in both
+        # (--profile-case: 304.5 MB read + 63.9 MB written for 8 heads of 33,272 tokens) scaled by
+        # heads x tokens; the operands of a head stay L2-resident in both
         # cases, so the traffic is the compulsory read of the records and the write of O.
         traffic = (304.453376e6 + 63.904768e6) / (8 * 33272) * heads_local * s_total
         line = {
@@ -414,6 +414,18 @@ def run_ours(args) -> None:
                          "peak_source": f"{peak_kind} bf16 GEMM {bf16} TFLOP/s x (1, 2, 4) for fp16, 8-bit, NVFP4 "
                                         "cells, weighted by executed FLOPs"},
         }
+        if world == 1:
+            from anemoi_b200 import native
+
+            # the library's own tcgen05 probe per MMA kind (128x128 tiles, no-swizzle operands)
+            kinds = {k: native.tensor_peak(k, device) for k in native.TENSOR_KINDS}
+            measured_mixed = (f4 + f8 + f16) / (f4 / kinds["nvfp4"] + f8 * 0.5 / kinds["i8"] +
+                                                f8 * 0.5 / kinds["f8"] + f16 / kinds["f16"])
+            line["roofline"]["tcgen05_measured"] = {
+                **{k: round(v, 1) for k, v in kinds.items()}, "mixed": round(measured_mixed, 1),
+                "frac_of_mixed": (achieved / measured_mixed) if achieved else None,
+                "note": "TFLOP/s of the library's tensor-pipe probe per kind; mixed = executed FLOPs weighted "
+                        "(QK of the 8-bit cell is kind::i8, its PV kind::f8f6f4)"}
         if world == 1 and not args.no_dense:
             line["dense_bf16"] = dense_flash_sample(q, k, v)
         if world == 1 and not args.no_cpu_baseline:

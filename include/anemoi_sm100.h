@@ -196,6 +196,19 @@ int anemoi_sm100_pack_qkv(const void* q, const void* k, const void* v, void* sen
 int anemoi_sm100_merge_heads(const void* recv, void* out, int64_t rows, int32_t ranks,
                              int32_t heads_per_rank, int32_t head_dim, void* stream);
 
+/* Measurement helper (no reference counterpart): throughput of the tcgen05 tensor pipe for one
+ * MMA kind, with the instruction forms, shared-memory operand layout and 128x128 tile of the
+ * attention kernel.  Launches 2 CTAs per SM that each issue 8*iterations MMAs; the caller times
+ * the launch with events on `stream`.  *flops = floating-point (or integer) operations the launch
+ * performs; *status (device int32, zeroed by the caller) becomes non-zero if a bounded wait gave
+ * up.  It gives the per-kind denominators of the attention roofline. */
+#define ANEMOI_SM100_KIND_F16 0
+#define ANEMOI_SM100_KIND_I8 1
+#define ANEMOI_SM100_KIND_F8 2
+#define ANEMOI_SM100_KIND_NVFP4 3
+int anemoi_sm100_tensor_peak(int32_t kind, int32_t iterations, int32_t* status, double* flops,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif
