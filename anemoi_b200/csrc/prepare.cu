@@ -40,6 +40,25 @@ struct PrepParams {
 
 template <typename InT>
 __device__ __forceinline__ uint4 load_narrow8(const InT* p);
+// 8 raw 16-bit elements -> 8 fp16 (bf16 through fp32, round to nearest even; fp16 unchanged)
+template <typename InT>
+__device__ __forceinline__ uint4 narrow8(uint4 raw);
+template <>
+__device__ __forceinline__ uint4 narrow8<__half>(uint4 raw) {
+  return raw;
+}
+template <>
+__device__ __forceinline__ uint4 narrow8<__nv_bfloat16>(uint4 raw) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  uint4 out;
+  __half2* h = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(b[i]);
+    h[i] = __floats2half2_rn(f.x, f.y);
+  }
+  return out;
+}
 
 template <>
 __device__ __forceinline__ uint4 load_narrow8<__half>(const __half* p) {
@@ -97,22 +116,41 @@ __device__ __forceinline__ int8_t int8_code(float x, float scale, float inv_scal
   return static_cast<int8_t>(__float2int_rz(t));
 }
 
-// Gathers `rows` rows into `tile` ([rows][D + kPad] halves), zero for invalid slots.
-template <typename InT, int D>
+// Gathers ROWS rows into `tile` ([ROWS][D + kPad] halves), zero for invalid slots.  The trip
+// count is a compile-time constant and the loop is split into a load pass and a store pass, so
+// every thread has all of its 16-byte loads (and the slot-index loads before them) in flight at
+// once: the kernel is bound by memory latency per CTA, not by arithmetic.
+template <typename InT, int D, int ROWS>
 __device__ __forceinline__ void gather_tile(__half* tile, const InT* src, const PrepParams& p,
-                                            int head, int rows, bool video, int first_slot,
-                                            int first_token, int valid_rows, int64_t token_stride,
+                                            int head, bool video, int first_slot, int first_token,
+                                            int valid_rows, int64_t token_stride,
                                             int64_t head_stride) {
   constexpr int kVec = D / 8;
-  for (int idx = threadIdx.x; idx < rows * kVec; idx += kThreads) {
+  constexpr int kIter = ROWS * kVec / kThreads;
+  static_assert(ROWS * kVec % kThreads == 0, "tile must be a multiple of the CTA's vector width");
+  int64_t token[kIter];
+#pragma unroll
+  for (int i = 0; i < kIter; ++i) {
+    const int r = (threadIdx.x + i * kThreads) / kVec;
+    token[i] = r < valid_rows
+                   ? (video ? (int64_t)p.s.prefix_tokens + __ldg(p.indices + first_slot + r)
+                            : (int64_t)first_token + r)
+                   : -1;
+  }
+  uint4 raw[kIter];
+#pragma unroll
+  for (int i = 0; i < kIter; ++i) {
+    const int c8 = (threadIdx.x + i * kThreads) % kVec;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (token[i] >= 0)
+      raw[i] = __ldg(reinterpret_cast<const uint4*>(src + token[i] * token_stride +
+                                                    (int64_t)head * head_stride + c8 * 8));
+  }
+#pragma unroll
+  for (int i = 0; i < kIter; ++i) {
+    const int idx = threadIdx.x + i * kThreads;
     const int r = idx / kVec, c8 = idx % kVec;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < valid_rows) {
-      const int64_t token =
-          video ? (int64_t)p.s.prefix_tokens + p.indices[first_slot + r] : (int64_t)first_token + r;
-      val = load_narrow8<InT>(src + token * token_stride + (int64_t)head * head_stride + c8 * 8);
-    }
-    *reinterpret_cast<uint4*>(tile + r * (D + kPad) + c8 * 8) = val;
+    *reinterpret_cast<uint4*>(tile + r * (D + kPad) + c8 * 8) = narrow8<InT>(raw[i]);
   }
 }
 
@@ -293,8 +331,8 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
     const bool video = task < R;
     const int t = video ? task : task - (2 * R + p.prefix_stages);
     const int valid = video ? p.counts[t] : min(QB, p.s.prefix_tokens - t * QB);
-    gather_tile<InT, D>(tile, q, p, head, QB, video, t * QB, t * QB, valid, p.stride[0],
-                        p.stride[1]);
+    gather_tile<InT, D, QB>(tile, q, p, head, video, t * QB, t * QB, valid, p.stride[0],
+                            p.stride[1]);
     __syncthreads();
     if (video) {
       __half* mean = static_cast<__half*>(p.o.q_pool) + ((int64_t)head * R + t) * D;
@@ -327,14 +365,16 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
   // ---------------- key/value block (video) or stage (prefix) ----------------
   const bool video = task < 2 * R;
   const int b = video ? task - R : task - 2 * R;
-  const int rows = video ? QB : 64;
   const int nst = video ? kF : 1;
   const int stage0 = video ? p.prefix_stages + b * kF : b;
   const int valid = video ? p.counts[b] : min(64, p.s.prefix_tokens - b * 64);
   const int64_t rec0 = (int64_t)head * p.stages + stage0;
 
-  gather_tile<InT, D>(tile, k, p, head, rows, video, b * QB, b * 64, valid, p.stride[2],
-                      p.stride[3]);
+  if (video) {
+    gather_tile<InT, D, QB>(tile, k, p, head, true, b * QB, 0, valid, p.stride[2], p.stride[3]);
+  } else {
+    gather_tile<InT, D, 64>(tile, k, p, head, false, 0, b * 64, valid, p.stride[2], p.stride[3]);
+  }
   __syncthreads();
   if (video) {
     __half* mean = static_cast<__half*>(p.o.k_pool) + ((int64_t)head * R + b) * D;
@@ -364,8 +404,11 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
   __syncthreads();
 
   // ---- values of the same rows ----
-  gather_tile<InT, D>(tile, v, p, head, rows, video, b * QB, b * 64, valid, p.stride[4],
-                      p.stride[5]);
+  if (video) {
+    gather_tile<InT, D, QB>(tile, v, p, head, true, b * QB, 0, valid, p.stride[4], p.stride[5]);
+  } else {
+    gather_tile<InT, D, 64>(tile, v, p, head, false, 0, b * 64, valid, p.stride[4], p.stride[5]);
+  }
   if (p.s.has_int8 && threadIdx.x < D) {
     const float amax =
         __half2float(__float2half_rn(p.o.v_amax[(int64_t)head * D + threadIdx.x]));
