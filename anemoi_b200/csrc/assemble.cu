@@ -76,10 +76,12 @@ int launch(const anemoi_sm100_shape& s, const void* prefix_out, int64_t prefix_r
 }
 
 // ---- Ulysses relayouts: pure 16-byte copies --------------------------------------------
-// q,k,v [rows][heads][D] (row / head strides in elements) -> send [ranks][rows][heads/ranks][3*D]
+// q,k,v [rows][heads][D] (row / head strides in elements) -> send [ranks][rows][heads_local][3*D],
+// where destination rank r receives its heads r*heads_per_rank + head_begin + (0..heads_local)
 __global__ void __launch_bounds__(256) pack_qkv_kernel(const uint16_t* q, const uint16_t* k,
                                                        const uint16_t* v, uint16_t* send,
-                                                       int64_t rows, int heads_local, int d8,
+                                                       int64_t rows, int heads_local,
+                                                       int heads_per_rank, int head_begin, int d8,
                                                        int64_t total, int64_t qs_row,
                                                        int64_t qs_head, int64_t ks_row,
                                                        int64_t ks_head, int64_t vs_row,
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const uint16_t* q, const 
     t /= heads_local;
     const int64_t row = t % rows;
     const int dest = (int)(t / rows);
-    const int gh = dest * heads_local + lh;
+    const int gh = dest * heads_per_rank + head_begin + lh;
     const uint16_t* src = which == 0 ? q + row * qs_row + gh * qs_head
                         : which == 1 ? k + row * ks_row + gh * ks_head
                                      : v + row * vs_row + gh * vs_head;
@@ -102,17 +104,18 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const uint16_t* q, const 
   }
 }
 
-// recv [ranks][rows][inner] -> out [rows][ranks][inner], inner = heads_local * D
+// recv [ranks][rows][inner] -> out [rows][ranks][outer] at element offset `begin8` of every
+// (row, rank) slot; inner = heads_local * D, outer = heads_per_rank * D (all in 16-byte units)
 __global__ void __launch_bounds__(256) merge_heads_kernel(const uint16_t* recv, uint16_t* out,
                                                           int64_t rows, int ranks, int inner8,
-                                                          int64_t total) {
+                                                          int outer8, int begin8, int64_t total) {
   for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * 256) {
     const int tail = (int)(idx % inner8);
     const int64_t slot = idx / inner8;
     const int source = (int)(slot % ranks);
     const int64_t row = slot / ranks;
-    *reinterpret_cast<uint4*>(out + idx * 8) =
+    *reinterpret_cast<uint4*>(out + (slot * outer8 + begin8 + tail) * 8) =
         __ldg(reinterpret_cast<const uint4*>(recv) + ((int64_t)source * rows + row) * inner8 + tail);
   }
 }
@@ -143,33 +146,54 @@ extern "C" int anemoi_sm100_assemble(const anemoi_sm100_shape* shape, const void
                                                 out_packed, inverse, row_counts, output, st);
 }
 
-extern "C" int anemoi_sm100_pack_qkv(const void* q, const void* k, const void* v, void* send,
-                                     int64_t rows, int32_t heads, int32_t head_dim, int32_t ranks,
-                                     const int64_t* strides, void* stream) {
+extern "C" int anemoi_sm100_pack_qkv_heads(const void* q, const void* k, const void* v, void* send,
+                                           int64_t rows, int32_t heads, int32_t head_dim,
+                                           int32_t ranks, int32_t head_begin, int32_t head_count,
+                                           const int64_t* strides, void* stream) {
   if (!q || !k || !v || !send || !strides || rows < 0 || heads <= 0 || ranks <= 0 ||
-      heads % ranks || head_dim % 8)
+      heads % ranks || head_dim % 8 || head_begin < 0 || head_count <= 0 ||
+      head_begin + head_count > heads / ranks)
     return ANEMOI_SM100_EINVAL;
   for (int i = 0; i < 6; ++i)
     if (strides[i] % 8) return ANEMOI_SM100_EINVAL;
-  const int64_t total = rows * heads * 3 * (head_dim / 8);
+  const int64_t total = rows * ranks * head_count * 3 * (head_dim / 8);
   if (total == 0) return ANEMOI_SM100_OK;
   const int blocks = (int)min((total + 255) / 256, (int64_t)(148 * 16));
   pack_qkv_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(k),
-      static_cast<const uint16_t*>(v), static_cast<uint16_t*>(send), rows, heads / ranks,
-      head_dim / 8, total, strides[0], strides[1], strides[2], strides[3], strides[4], strides[5]);
+      static_cast<const uint16_t*>(v), static_cast<uint16_t*>(send), rows, head_count,
+      heads / ranks, head_begin, head_dim / 8, total, strides[0], strides[1], strides[2],
+      strides[3], strides[4], strides[5]);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+extern "C" int anemoi_sm100_pack_qkv(const void* q, const void* k, const void* v, void* send,
+                                     int64_t rows, int32_t heads, int32_t head_dim, int32_t ranks,
+                                     const int64_t* strides, void* stream) {
+  if (ranks <= 0 || heads <= 0 || heads % ranks) return ANEMOI_SM100_EINVAL;
+  return anemoi_sm100_pack_qkv_heads(q, k, v, send, rows, heads, head_dim, ranks, 0, heads / ranks,
+                                     strides, stream);
+}
+
+extern "C" int anemoi_sm100_merge_heads_into(const void* recv, void* out, int64_t rows,
+                                             int32_t ranks, int32_t head_count, int32_t head_dim,
+                                             int32_t heads_per_rank, int32_t head_begin,
+                                             void* stream) {
+  if (!recv || !out || rows < 0 || ranks <= 0 || head_count <= 0 || head_dim % 8 ||
+      head_begin < 0 || head_begin + head_count > heads_per_rank)
+    return ANEMOI_SM100_EINVAL;
+  const int inner8 = head_count * head_dim / 8;
+  const int64_t total = rows * ranks * inner8;
+  if (total == 0) return ANEMOI_SM100_OK;
+  const int blocks = (int)min((total + 255) / 256, (int64_t)(148 * 16));
+  merge_heads_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(recv), static_cast<uint16_t*>(out), rows, ranks, inner8,
+      heads_per_rank * head_dim / 8, head_begin * head_dim / 8, total);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
 
 extern "C" int anemoi_sm100_merge_heads(const void* recv, void* out, int64_t rows, int32_t ranks,
                                         int32_t heads_per_rank, int32_t head_dim, void* stream) {
-  if (!recv || !out || rows < 0 || ranks <= 0 || heads_per_rank <= 0 || head_dim % 8)
-    return ANEMOI_SM100_EINVAL;
-  const int inner8 = heads_per_rank * head_dim / 8;
-  const int64_t total = rows * ranks * inner8;
-  if (total == 0) return ANEMOI_SM100_OK;
-  const int blocks = (int)min((total + 255) / 256, (int64_t)(148 * 16));
-  merge_heads_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(recv), static_cast<uint16_t*>(out), rows, ranks, inner8, total);
-  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+  return anemoi_sm100_merge_heads_into(recv, out, rows, ranks, heads_per_rank, head_dim,
+                                       heads_per_rank, 0, stream);
 }

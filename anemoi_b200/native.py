@@ -83,6 +83,9 @@ def library() -> C.CDLL:
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
         "anemoi_sm100_pack_qkv": (C.c_int, [P, P, P, P, I64, I32, I32, I32, C.POINTER(I64), P]),
         "anemoi_sm100_merge_heads": (C.c_int, [P, P, I64, I32, I32, I32, P]),
+        "anemoi_sm100_pack_qkv_heads": (C.c_int, [P, P, P, P, I64, I32, I32, I32, I32, I32,
+                                                  C.POINTER(C.c_int64), P]),
+        "anemoi_sm100_merge_heads_into": (C.c_int, [P, P, I64, I32, I32, I32, I32, I32, P]),
         "anemoi_sm100_tensor_peak": (C.c_int, [I32, I32, P, C.POINTER(C.c_double), P]),
     }
     for name, (restype, argtypes) in signatures.items():
@@ -100,7 +103,8 @@ EXPORTED = (
     "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
-    "anemoi_sm100_merge_heads", "anemoi_sm100_tensor_peak",
+    "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
+    "anemoi_sm100_tensor_peak",
 )
 
 
@@ -274,8 +278,12 @@ def assemble(shape: Shape, prefix_out: torch.Tensor | None, out_packed: torch.Te
     return out
 
 
-def pack_qkv_destination_major(q, k, v, world: int) -> torch.Tensor:
-    """``(rows, heads, D)`` x3 (strided views allowed) -> ``(world, rows, heads/world, 3*D)``."""
+def pack_qkv_destination_major(q, k, v, world: int, head_begin: int = 0,
+                               head_count: int | None = None) -> torch.Tensor:
+    """``(rows, heads, D)`` x3 (strided views allowed) -> ``(world, rows, head_count, 3*D)``.
+
+    Destination rank ``r`` gets its heads ``r*heads/world + head_begin + (0..head_count)``
+    (default: all ``heads/world`` of them)."""
     rows, heads, d = q.shape
     if heads % world:
         raise ValueError(f"heads ({heads}) must divide the Ulysses degree ({world})")
@@ -283,26 +291,41 @@ def pack_qkv_destination_major(q, k, v, world: int) -> torch.Tensor:
         raise ValueError("q, k, v must share shape and dtype")
     if q.element_size() != 2 or any(t.stride(-1) != 1 for t in (q, k, v)):
         raise ValueError("pack_qkv needs 16-bit tensors with a contiguous head dimension")
-    out = torch.empty((world, rows, heads // world, 3 * d), dtype=q.dtype, device=q.device)
+    head_count = heads // world - head_begin if head_count is None else head_count
+    if head_begin < 0 or head_count <= 0 or head_begin + head_count > heads // world:
+        raise ValueError("head range outside the heads of a rank")
+    out = torch.empty((world, rows, head_count, 3 * d), dtype=q.dtype, device=q.device)
     if out.numel() == 0:
         return out
     strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
-    _check(library().anemoi_sm100_pack_qkv(_ptr(q), _ptr(k), _ptr(v), _ptr(out), rows, heads, d,
-                                           world, strides, _stream(q.device)),
-           "anemoi_sm100_pack_qkv")
+    _check(library().anemoi_sm100_pack_qkv_heads(_ptr(q), _ptr(k), _ptr(v), _ptr(out), rows, heads, d,
+                                                 world, head_begin, head_count, strides,
+                                                 _stream(q.device)),
+           "anemoi_sm100_pack_qkv_heads")
     return out
 
 
-def merge_heads(x: torch.Tensor) -> torch.Tensor:
-    """``(world, rows, heads_local, D)`` contiguous -> ``(rows, world*heads_local, D)``."""
-    world, rows, hl, d = x.shape
+def merge_heads(x: torch.Tensor, out: torch.Tensor | None = None, head_begin: int = 0) -> torch.Tensor:
+    """``(world, rows, head_count, D)`` contiguous -> ``(rows, world*heads_per_rank, D)``.
+
+    Without ``out`` the result holds exactly the given heads; with ``out`` (contiguous) the heads
+    land at ``head_begin`` of every rank's ``out.size(1) // world`` heads."""
+    world, rows, hc, d = x.shape
     if not x.is_contiguous() or x.element_size() != 2:
         raise ValueError("merge_heads needs a contiguous 16-bit tensor")
-    out = torch.empty((rows, world * hl, d), dtype=x.dtype, device=x.device)
-    if out.numel() == 0:
+    if out is None:
+        out = torch.empty((rows, world * hc, d), dtype=x.dtype, device=x.device)
+    if (not out.is_contiguous() or out.dtype != x.dtype or out.size(0) != rows or out.size(2) != d
+            or out.size(1) % world):
+        raise ValueError("merge_heads: out must be contiguous (rows, world*heads_per_rank, D)")
+    per_rank = out.size(1) // world
+    if head_begin < 0 or head_begin + hc > per_rank:
+        raise ValueError("head range outside the heads of a rank")
+    if x.numel() == 0:
         return out
-    _check(library().anemoi_sm100_merge_heads(_ptr(x), _ptr(out), rows, world, hl, d,
-                                              _stream(x.device)), "anemoi_sm100_merge_heads")
+    _check(library().anemoi_sm100_merge_heads_into(_ptr(x), _ptr(out), rows, world, hc, d, per_rank,
+                                                   head_begin, _stream(x.device)),
+           "anemoi_sm100_merge_heads_into")
     return out
 
 

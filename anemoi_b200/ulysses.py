@@ -90,36 +90,83 @@ def exchange_to_sequence(out_heads, counts, rank: int, group=None, merge=native.
     return merge(recv)
 
 
+def head_groups(heads_local: int, groups: int) -> list[tuple[int, int]]:
+    """``(begin, count)`` of at most ``groups`` contiguous, near-equal groups of a rank's heads."""
+    groups = max(1, min(groups, heads_local))
+    base, extra = divmod(heads_local, groups)
+    out, begin = [], 0
+    for g in range(groups):
+        count = base + (1 if g < extra else 0)
+        out.append((begin, count))
+        begin += count
+    return out
+
+
 def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_destination_major,
-                      merge=native.merge_heads):
-    """Head-shard, run ``attention_fn(q, k, v)`` on ``[1, S, H/world, D]`` views, shard back.
+                      merge=native.merge_heads, pipeline_groups: int = 2):
+    """Head-shard, run ``attention_fn(q, k, v)`` on ``[1, S, h, D]`` views, shard back.
 
     ``q, k, v``: ``[1, rows_local, H, D]`` (this rank's rows, every head).  Returns
-    ``[1, rows_local, H, D]``."""
+    ``[1, rows_local, H, D]``.
+
+    The rank's ``H/world`` heads are processed in ``pipeline_groups`` groups.  All input
+    exchanges are issued up front as asynchronous collectives, each group's attention waits only
+    for its own exchange, and its output exchange runs while the next group computes: apart from
+    the first group's input and the last group's output, the all-to-all traffic overlaps the
+    attention kernels.  Every rank issues the same collectives in the same order."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return attention_fn(q, k, v)
     rank = dist.get_rank(group)
-    heads, d = q.size(2), q.size(3)
+    rows, heads, d = q.size(1), q.size(2), q.size(3)
     if heads % world:
         raise ValueError(f"heads ({heads}) must divide the Ulysses degree ({world})")
-    counts = row_counts(q.size(1), group)
-    packed = exchange_to_heads(q[0], k[0], v[0], counts, group, pack)    # (S, h, 3D)
-    qh, kh, vh = (packed[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
-    out = attention_fn(qh, kh, vh)                                       # [1, S, h, D]
-    return exchange_to_sequence(out[0].contiguous(), counts, rank, group, merge).unsqueeze(0)
+    h_local = heads // world
+    counts = row_counts(rows, group)
+    total = sum(counts)
+    parts = head_groups(h_local, pipeline_groups)
+
+    inbound = []
+    for begin, count in parts:
+        send = pack(q[0], k[0], v[0], world, begin, count)           # (world, rows, count, 3D)
+        inner = count * 3 * d
+        recv = torch.empty((total, count, 3 * d), dtype=q.dtype, device=q.device)
+        work = dist.all_to_all_single(recv.view(-1), send.view(-1),
+                                      output_split_sizes=[c * inner for c in counts],
+                                      input_split_sizes=[rows * inner] * world, group=group,
+                                      async_op=True)
+        inbound.append((work, recv, send))
+
+    out = torch.empty((rows, heads, d), dtype=q.dtype, device=q.device)
+    outbound = []
+    for (begin, count), (work, recv, send) in zip(parts, inbound):
+        work.wait()
+        qh, kh, vh = (recv[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
+        result = attention_fn(qh, kh, vh)[0].contiguous()            # (S, count, D)
+        inner = count * d
+        back = torch.empty((world, rows, count, d), dtype=q.dtype, device=q.device)
+        work = dist.all_to_all_single(back.view(-1), result.view(-1),
+                                      output_split_sizes=[rows * inner] * world,
+                                      input_split_sizes=[c * inner for c in counts], group=group,
+                                      async_op=True)
+        outbound.append((work, back, result, begin))
+    for work, back, result, begin in outbound:
+        work.wait()
+        merge(back, out, begin)
+    return out.unsqueeze(0)
 
 
 def ulysses_anemoi_attention(q, k, v, *, layout: VisualLayout, layer: int,
                              sparse_config: SparseConfig | None = None,
                              quant_config: QuantConfig | None = None,
-                             calibration: NVFP4Calibration | None = None, group=None):
+                             calibration: NVFP4Calibration | None = None, group=None,
+                             pipeline_groups: int = 2):
     """``anemoi_attention`` with the heads sharded over the ranks of ``group``."""
     def local(qh, kh, vh):
         return anemoi_attention(qh, kh, vh, layout=layout, layer=layer, sparse_config=sparse_config,
                                 quant_config=quant_config, calibration=calibration)
-    return ulysses_attention(q, k, v, local, group)
+    return ulysses_attention(q, k, v, local, group, pipeline_groups=pipeline_groups)
 
 
-__all__ = ["shard_rows", "row_counts", "reset_row_counts", "exchange_to_heads",
+__all__ = ["shard_rows", "row_counts", "reset_row_counts", "head_groups", "exchange_to_heads",
            "exchange_to_sequence", "ulysses_attention", "ulysses_anemoi_attention"]

@@ -405,7 +405,9 @@ def run_ours(args) -> None:
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in (q, k, v))),
                     "d2h_bytes_per_step": int(out.numel() * out.element_size())},
-            "gpu_launches": 10 + (2 if world > 1 else 0),
+            # 10 library kernels per attention call; with N > 1 the local heads run as pipelined
+            # groups, each with its own pack and merge kernel
+            "gpu_launches": 10 if world == 1 else 12 * len(ulysses.head_groups(w["heads"] // world, 2)),
             "stage_ms": stages,
             "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
                          "achieved": achieved, "peak": mixed_peak, "unit": "TFLOP/s",

@@ -195,6 +195,20 @@ int anemoi_sm100_pack_qkv(const void* q, const void* k, const void* v, void* sen
                           void* stream);
 int anemoi_sm100_merge_heads(const void* recv, void* out, int64_t rows, int32_t ranks,
                              int32_t heads_per_rank, int32_t head_dim, void* stream);
+/* The same relayouts for a sub-range of every rank's heads, so that the exchange of one group of
+ * heads can overlap the attention of another (head-group pipelining; the reference exchanges all
+ * heads at once, ulysses_custom.py:107-165):
+ * pack : send [ranks][rows][head_count][3*D] takes, for destination rank r, the heads
+ *        r*(heads/ranks) + head_begin + (0..head_count)
+ * merge: recv [ranks][rows][head_count][D] lands in out [rows][ranks*heads_per_rank][D] at heads
+ *        r*heads_per_rank + head_begin + (0..head_count) */
+int anemoi_sm100_pack_qkv_heads(const void* q, const void* k, const void* v, void* send,
+                                int64_t rows, int32_t heads, int32_t head_dim, int32_t ranks,
+                                int32_t head_begin, int32_t head_count, const int64_t* strides,
+                                void* stream);
+int anemoi_sm100_merge_heads_into(const void* recv, void* out, int64_t rows, int32_t ranks,
+                                  int32_t head_count, int32_t head_dim, int32_t heads_per_rank,
+                                  int32_t head_begin, void* stream);
 
 /* Measurement helper (no reference counterpart): throughput of the tcgen05 tensor pipe for one
  * MMA kind, with the instruction forms, shared-memory operand layout and 128x128 tile of the

@@ -21,6 +21,16 @@ def test_pack_and_merge_equal_torch_permutes(native_library):
         assert torch.equal(got.cpu(), want)
         x = torch.randn(world, rows, heads // world, d, generator=gen).to(torch.float16).cuda()
         assert torch.equal(native.merge_heads(x).cpu(), torch_merge(x.cpu()))
+        # a sub-range of every rank's heads (head-group pipelining of the exchange)
+        hl = heads // world
+        if hl >= 2 and rows:
+            begin, count = 1, hl - 1
+            got = native.pack_qkv_destination_major(q, k, v, world, begin, count)
+            assert torch.equal(got.cpu(), torch_pack(q.cpu(), k.cpu(), v.cpu(), world, begin, count))
+            part = torch.randn(world, rows, count, d, generator=gen).to(torch.float16).cuda()
+            out = torch.zeros(rows, heads, d, dtype=torch.float16, device="cuda")
+            native.merge_heads(part, out, begin)
+            assert torch.equal(out.cpu(), torch_merge(part.cpu(), torch.zeros(rows, heads, d, dtype=torch.float16), begin))
     with pytest.raises(ValueError):
         native.pack_qkv_destination_major(q, k, v, 3)
 

@@ -13,18 +13,23 @@ import torch.multiprocessing as mp
 from anemoi_b200 import ulysses
 
 
-def torch_pack(q, k, v, world):
+def torch_pack(q, k, v, world, begin=0, count=None):
     rows, heads, d = q.shape
     hl = heads // world
-    out = torch.empty((world, rows, hl, 3 * d), dtype=q.dtype)
+    count = hl - begin if count is None else count
+    out = torch.empty((world, rows, count, 3 * d), dtype=q.dtype)
     for i, t in enumerate((q, k, v)):
-        out[..., i * d : (i + 1) * d] = t.reshape(rows, world, hl, d).permute(1, 0, 2, 3)
+        out[..., i * d : (i + 1) * d] = t.reshape(rows, world, hl, d)[:, :, begin : begin + count].permute(1, 0, 2, 3)
     return out
 
 
-def torch_merge(x):
-    world, rows, hl, d = x.shape
-    return x.permute(1, 0, 2, 3).contiguous().reshape(rows, world * hl, d)
+def torch_merge(x, out=None, begin=0):
+    world, rows, hc, d = x.shape
+    if out is None:
+        out = torch.empty((rows, world * hc, d), dtype=x.dtype)
+    per_rank = out.size(1) // world
+    out.view(rows, world, per_rank, d)[:, :, begin : begin + hc] = x.permute(1, 0, 2, 3)
+    return out
 
 
 def toy_attention(q, k, v):
@@ -43,9 +48,12 @@ def _worker(rank, world, port, total_rows, heads, d, results):
         rows = ulysses.shard_rows(total_rows, world)
         lo = sum(rows[:rank])
         mine = [t[:, lo : lo + rows[rank]].contiguous() for t in full]
-        got = ulysses.ulysses_attention(*mine, toy_attention, pack=torch_pack, merge=torch_merge)
         want = toy_attention(*full)[:, lo : lo + rows[rank]]
-        ok = torch.equal(got, want)
+        ok = True
+        for groups in (1, 2, 3):  # one exchange, pipelined head groups, more groups than heads
+            got = ulysses.ulysses_attention(*mine, toy_attention, pack=torch_pack, merge=torch_merge,
+                                            pipeline_groups=groups)
+            ok = ok and torch.equal(got, want)
         counts = ulysses.row_counts(rows[rank])
         # a changed local length without a reset must fail loudly, not desynchronise
         raised = False
@@ -77,3 +85,14 @@ def test_shard_rows_matches_tensor_split():
     for total, world in ((38247, 4), (85184, 8), (7, 8), (33272, 8)):
         want = [t.numel() for t in torch.tensor_split(torch.arange(total), world)]
         assert ulysses.shard_rows(total, world) == want
+
+
+def test_head_groups_cover_the_local_heads():
+    assert ulysses.head_groups(7, 2) == [(0, 4), (4, 3)]
+    assert ulysses.head_groups(28, 2) == [(0, 14), (14, 14)]
+    assert ulysses.head_groups(1, 2) == [(0, 1)]
+    assert ulysses.head_groups(5, 1) == [(0, 5)]
+    for heads, groups in ((7, 3), (56, 4), (2, 8)):
+        parts = ulysses.head_groups(heads, groups)
+        assert parts[0][0] == 0 and sum(c for _, c in parts) == heads
+        assert all(parts[i][0] + parts[i][1] == parts[i + 1][0] for i in range(len(parts) - 1))
