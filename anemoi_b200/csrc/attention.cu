@@ -4,7 +4,8 @@
 // shape) and walks that tile's ragged list of 64-key stages in the order
 // NVFP4 -> INT8 -> FP16 with one online-softmax state.
 //
-// Warp roles (192 threads):
+// Warp roles (256 threads = two warpgroups; the second one gives most of its registers to the
+// first with setmaxnreg, so a softmax thread may use 192 registers at two CTAs per SM):
 //   warps 0-3  softmax: warp w owns TMEM lanes 32*w.. (query rows); one thread per row holds
 //              the row's 64 scores of a stage in registers (few threads with long unrolled
 //              instruction streams: the per-stage fixed cost is paid once per row)
@@ -15,6 +16,7 @@
 //                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
 //                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
 //              and tcgen05.commit to mbarriers
+//   warps 6-7  idle (they complete the second warpgroup)
 // TMEM columns: S0 [0,64), O [64,64+D), and [192,256) holds the NVFP4 scale factors in the
 // NVFP4 phase and a second score buffer S1 in the INT8 / FP16 phases (QK of stage g+1 runs
 // while the softmax threads still read the scores of stage g).
@@ -48,7 +50,9 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;         // two warpgroups: softmax | loader, MMA and two idle warps
+constexpr int kSoftmaxRegs = 192;     // 128 * 192 + 128 * 64 == 256 * 128 (two CTAs per SM)
+constexpr int kOtherRegs = 64;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kLoaderWarp = 4;
 constexpr int kMmaWarp = 5;
@@ -202,23 +206,26 @@ struct RowState {
   float m, d;
 };
 
-// O[row][c] *= alpha (* colf[c] when kColf) for all D columns of the thread's row.
+// O[row][c] *= alpha (* colf[c] when kColf) for all D columns of the thread's row, 64 columns
+// (two TMEM loads in flight) per step.
 template <int D, bool kColf>
 __device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const float* colf) {
   const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll 1
-  for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t r[32];
-    tmem_ld32(tmem_row + kColO + c0, r);
+  for (int c0 = 0; c0 < D; c0 += 64) {
+    uint32_t r[64];
+    tmem_ld32(tmem_row + kColO + c0, *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_ld32(tmem_row + kColO + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 32; j += 2) {
+    for (int j = 0; j < 64; j += 2) {
       float2 v = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), alpha2);
       if (kColf) v = fmul2(v, *reinterpret_cast<const float2*>(colf + c0 + j));
       r[j] = __float_as_uint(v.x);
       r[j + 1] = __float_as_uint(v.y);
     }
-    tmem_st32(tmem_row + kColO + c0, r);
+    tmem_st32(tmem_row + kColO + c0, *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_st32(tmem_row + kColO + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
   }
   tmem_wait_st();
 }
@@ -534,6 +541,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : tile);
   const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
 
+  // The second warpgroup (loader, MMA and two idle warps) hands most of its registers to the
+  // softmax warpgroup.  All four warps of a warpgroup execute the same setmaxnreg instruction,
+  // and each sits at the top of the branch whose code runs under the new register count.
+  if (warp >= kLoaderWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
   if (warp == kLoaderWarp) {
     // =============================== loader ===============================
     // The whole warp walks the list with uniform control flow; one lane issues.
@@ -649,7 +661,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     }
     // The end of the tile is signalled on a barrier of its own.
     mma_commit(&b->all_done, lead);
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     // =============================== softmax rows ===============================
     const int row = warp * 32 + lane;            // query row == TMEM lane
     const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
