@@ -440,6 +440,87 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------
+# kernel sweep (the fourth benchmark configuration): not a bench line, a table
+# ------------------------------------------------------------------------------------------
+SWEEP_CELLS = {"nvfp4": (1.0, 0.0, 0.0), "int8": (0.0, 1.0, 0.0), "fp16": (0.0, 0.0, 1.0),
+               "nvfp4+int8": (0.5, 0.5, 0.0), "nvfp4+fp16": (0.5, 0.0, 0.5),
+               "int8+fp16": (0.0, 0.5, 0.5), "nvfp4+int8+fp16": (0.4, 0.4, 0.2)}
+
+
+def run_sweep(args) -> None:
+    """Visual-only 21x48x84 layer over D x query block x drop ratio x cells (x maxpool weight for
+    the mixed cell), `--sweep-heads` heads per point.  One JSON line per point: stage times,
+    preparation and routing GB/s (algorithmic bytes / CUDA-event time) and the attention
+    kernel's executed FLOPs against the mixed tensor peak.  Writes `--sweep-out` as well."""
+    from anemoi_b200 import executor
+    from anemoi_b200.build import build
+    from anemoi_b200.layout import materialize_ragged_2d_layout
+    from anemoi_b200.routing import route_counts
+
+    build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    bf16 = float(peaks["bf16_tflops"])
+    video, heads = (21, 48, 84), args.sweep_heads
+    s_total = math.prod(video)
+    rows = []
+    for d in (64, 128):
+        w = dict(WORKLOAD, prefix=0, video=video, dim=d, outliers=(17, 53) if d == 64 else (17, 93))
+        q, k, v = synth_qkv(w, heads, device, seed=0)
+        scales = tuple(float(t.float().abs().max()) / (6 * 448) for t in (q, k, v))
+        for qb in (64, 128):
+            blocks = materialize_ragged_2d_layout("cpu", frames=video[0], height=video[1], width=video[2],
+                                                  logical_block=qb).video_blocks
+            for drop in (0.5, 0.8, 0.9):
+                for cell, ratios in SWEEP_CELLS.items():
+                    for weight in ((0.0, 0.5, 1.0) if cell == "nvfp4+int8+fp16" else (0.0,)):
+                        def call():
+                            return executor.sm100_ragged_attention(
+                                q, k, v, prefix_tokens=0, sparsity_ratio=drop,
+                                retained_nvfp4_ratio=ratios[0], retained_int8_ratio=ratios[1],
+                                retained_fp16_ratio=ratios[2], video_shape=video, layer=0,
+                                query_block_size=qb, maxpool_weight=weight,
+                                nvfp4_scales=scales if ratios[0] > 0 else (1.0, 1.0, 1.0),
+                                return_parts=True)
+                        call()
+                        executor.collect_stage_events(True)
+                        out, parts = call()
+                        st = executor.stage_times_ms()
+                        executor.collect_stage_events(False)
+                        if executor.last_status(device) != 0 or not bool(torch.isfinite(out).all()):
+                            raise SystemExit(f"sweep point failed: D={d} Q={qb} drop={drop} {cell}")
+                        n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=drop, nvfp4_ratio=ratios[0],
+                                                   int8_ratio=ratios[1], fp16_ratio=ratios[2])
+                        f4, f8, f16 = (4.0 * d * heads * n * qb * qb for n in (n4, n8, n16))
+                        mixed = (f4 + f8 + f16) / (f4 / (4 * bf16) + f8 / (2 * bf16) + f16 / bf16)
+                        store = parts["store"].buffers
+                        rec_bytes = sum(t.numel() * t.element_size() for t in store.values() if t is not None)
+                        in_bytes = 3 * q.numel() * q.element_size() + (v.numel() * 2 if ratios[1] > 0 else 0)
+                        route_bytes = (4 * heads * blocks * blocks * 2 + 2 * heads * blocks * d * 2 * (2 if weight else 1)
+                                       + parts["lists"].stage_ids.numel() * 4)
+                        row = {"D": d, "Q": qb, "drop": drop, "cell": cell, "maxpool": weight, "heads": heads,
+                               "stage_ms": {kk: round(vv, 4) for kk, vv in st.items()},
+                               "prepare_GBs": round((in_bytes + rec_bytes) / (st["prepare"] * 1e-3) / 1e9, 1),
+                               "routing_GBs": round(route_bytes / ((st["draft"] + st["route"]) * 1e-3) / 1e9, 1),
+                               "attention_TFLOPs": round((f4 + f8 + f16) / (st["attention"] * 1e-3) / 1e12, 1),
+                               "attention_frac_of_mixed_peak": round((f4 + f8 + f16) / (st["attention"] * 1e-3) / 1e12 / mixed, 3)}
+                        rows.append(row)
+                        print(json.dumps(row), flush=True)
+    if args.sweep_out:
+        with open(args.sweep_out, "w") as fh:
+            fh.write(f"# kernel sweep, visual-only 21x48x84 (S={s_total}), {heads} heads per point, "
+                     f"peak = {peak_kind} bf16 {bf16} TFLOP/s x (1,2,4)\n\n")
+            fh.write("| D | Q | drop | cell | maxpool | prepare ms | prepare GB/s | draft+route ms | routing GB/s | "
+                     "attention ms | executed TFLOP/s | frac of mixed peak |\n|---|---|---|---|---|---|---|---|---|---|---|---|\n")
+            for r in rows:
+                t = r["stage_ms"]
+                fh.write(f"| {r['D']} | {r['Q']} | {r['drop']} | {r['cell']} | {r['maxpool']} | {t['prepare']:.3f} | "
+                         f"{r['prepare_GBs']} | {t['draft'] + t['route']:.3f} | {r['routing_GBs']} | {t['attention']:.3f} | "
+                         f"{r['attention_TFLOPs']} | {r['attention_frac_of_mixed_peak']} |\n")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -449,12 +530,17 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-dense", action="store_true",
                     help="skip the dense bf16 library attention timed beside the sparse layer")
+    ap.add_argument("--sweep", action="store_true", help="run the kernel sweep instead of the benchmark")
+    ap.add_argument("--sweep-heads", type=int, default=4)
+    ap.add_argument("--sweep-out", default="")
     ap.add_argument("--profile-case", action="store_true",
                     help="run the small profiling case instead of the benchmark workload")
     args = ap.parse_args()
     if args.profile_case:
         WORKLOAD.update(PROFILE_WORKLOAD)
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
