@@ -390,10 +390,10 @@ def run_ours(args) -> None:
         attn_ms = stages.get("attention", float("nan"))
         achieved = video_flops / (attn_ms * 1e-3) / 1e12 if attn_ms == attn_ms else None
         # DRAM traffic of one video-attention launch: the ncu capture of the small profiling case
-        # (--profile-case: 304.5 MB read + 63.9 MB written for 8 heads of 33,272 tokens) scaled by
+        # (--profile-case: 305.6 MB read + 71.3 MB written for 8 heads of 33,272 tokens) scaled by
         # heads x tokens; the operands of a head stay L2-resident in both
         # cases, so the traffic is the compulsory read of the records and the write of O.
-        traffic = (304.453376e6 + 63.904768e6) / (8 * 33272) * heads_local * s_total
+        traffic = (305.575168e6 + 71.335680e6) / (8 * 33272) * heads_local * s_total
         line = {
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
