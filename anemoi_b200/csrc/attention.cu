@@ -92,7 +92,8 @@ struct Barriers {
   uint64_t kv_full[kMaxSlots];
   uint64_t kv_free[kMaxSlots];
   uint64_t q_full, q_free;
-  uint64_t s_full[2], s_free[2];  // per score buffer
+  uint64_t s_full[2];  // scores ready, per score buffer
+  uint64_t s_free;     // scores read by the softmax warps (NVFP4 phase: single buffer)
   uint64_t all_done;  // every MMA of the tile complete (epilogue)
   // Two P barriers used alternately: a warp that skips the wait for the previous PV may run one stage
   // ahead, and its arrival must not be counted into the previous stage's phase.
@@ -294,7 +295,7 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
   if (!live_warp) {
     // padding rows of a 64-row tile: keep the barrier protocol, skip the math
     if (lead) {
-      mbar_arrive(&b->s_free[sb]);
+      if (cell == kNv) mbar_arrive(&b->s_free);
       mbar_arrive(&b->p_full[g & 1]);
     }
     return;
@@ -305,9 +306,14 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
     tmem_ld32(tmem_row + s_column(sb), *reinterpret_cast<uint32_t(*)[32]>(r));
     tmem_ld32(tmem_row + s_column(sb) + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
     tmem_wait_ld();
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lead) mbar_arrive(&b->s_free[sb]);
+    if (cell == kNv) {
+      // Only the NVFP4 phase has a single score buffer, whose release the MMA warp must see
+      // before the next QK.  With two buffers, QK of stage g+2 is issued after the MMA warp has
+      // waited for P of stage g, which every softmax thread writes after this load.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lead) mbar_arrive(&b->s_free);
+    }
     if (cell == kI8) {
       // Scores are s32; as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, so
       // the conversion is an integer add and a float subtract (no conversion instruction).
@@ -517,8 +523,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     mbar_init(&b->q_free, 1);
     mbar_init(&b->s_full[0], 1);
     mbar_init(&b->s_full[1], 1);
-    mbar_init(&b->s_free[0], kSoftmaxThreads / 32);
-    mbar_init(&b->s_free[1], kSoftmaxThreads / 32);
+    mbar_init(&b->s_free, kSoftmaxThreads / 32);
     mbar_init(&b->p_full[0], kSoftmaxThreads / 32);
     mbar_init(&b->p_full[1], kSoftmaxThreads / 32);
     mbar_init(&b->all_done, 1);
@@ -607,7 +612,6 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     const uint32_t lead = lane == 0;
     int g = 0, phase_ord = 0;
     uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
-    int s_use0 = 0, s_use1 = 0;  // QK launches into each score buffer so far
     const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
     for (int cell = 0; cell < 3; ++cell) {
       if (cnt[cell] == 0) continue;
@@ -634,10 +638,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           wait<50>(b, &b->kv_full[slot], (usepar >> slot) & 1u, p.status, 4);
           usepar ^= 1u << slot;
           const int sb = s_buffer(cell, gi);
-          const int s_used = sb ? s_use1 : s_use0;
-          if (s_used > 0) wait<50>(b, &b->s_free[sb], (s_used - 1) & 1, p.status, 5);
-          s_use0 += sb ? 0 : 1;
-          s_use1 += sb ? 1 : 0;
+          // single score buffer of the NVFP4 phase (always the first phase: gi == i)
+          if (cell == kNv && i > 0) wait<50>(b, &b->s_free, (uint32_t)(i - 1) & 1u, p.status, 5);
           tc_fence_after_sync();
           const uint32_t slot_addr = ring_addr + slot * slot_bytes;
           issue_qk<D>(cell, tmem + s_column(sb), tmem, q_addr, slot_addr, slot_addr, lead);
