@@ -87,6 +87,8 @@ def library() -> C.CDLL:
                                                   C.POINTER(C.c_int64), P]),
         "anemoi_sm100_merge_heads_into": (C.c_int, [P, P, I64, I32, I32, I32, I32, I32, P]),
         "anemoi_sm100_tensor_peak": (C.c_int, [I32, I32, P, C.POINTER(C.c_double), P]),
+        "anemoi_sm100_qknorm_rope": (C.c_int, [P, P, P, P, I64, I32, I32, I32, C.c_float, I32,
+                                               C.POINTER(C.c_int64), P]),
     }
     for name, (restype, argtypes) in signatures.items():
         fn = getattr(lib, name)
@@ -104,7 +106,7 @@ EXPORTED = (
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
-    "anemoi_sm100_tensor_peak",
+    "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope",
 )
 
 
@@ -358,3 +360,24 @@ def tensor_peak(kind: str, device=None, iterations: int = 4096, repeats: int = 3
     if int(status.item()) != 0:
         raise RuntimeError("anemoi_sm100_tensor_peak: a bounded wait gave up")
     return best
+
+
+def qknorm_rope_(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 eps: float) -> torch.Tensor:
+    """In place: per-head RMS norm with ``weight`` then partial rotary on ``x`` ``[tokens, heads, D]``
+    (strided views with a contiguous last dimension are fine); ``cos``/``sin`` ``[tokens, rotary]``."""
+    if x.ndim != 3 or x.dtype not in (torch.float16, torch.bfloat16) or x.stride(-1) != 1:
+        raise ValueError("x must be [tokens, heads, D] fp16/bf16 with a contiguous head dimension")
+    tokens, heads, d = x.shape
+    if weight.shape != (d,) or weight.dtype != x.dtype or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous [D] tensor of x's dtype")
+    if cos.shape != sin.shape or cos.ndim != 2 or cos.size(0) != tokens:
+        raise ValueError("cos and sin must be [tokens, rotary_dim]")
+    cos = cos.to(device=x.device, dtype=torch.float32).contiguous()
+    sin = sin.to(device=x.device, dtype=torch.float32).contiguous()
+    strides = (C.c_int64 * 2)(x.stride(0), x.stride(1))
+    _check(library().anemoi_sm100_qknorm_rope(_ptr(x), _ptr(weight), _ptr(cos), _ptr(sin), tokens, heads, d,
+                                              cos.size(1), float(eps), int(x.dtype == torch.bfloat16),
+                                              strides, _stream(x.device)),
+           "anemoi_sm100_qknorm_rope")
+    return x

@@ -210,6 +210,17 @@ int anemoi_sm100_merge_heads_into(const void* recv, void* out, int64_t rows, int
                                   int32_t head_count, int32_t head_dim, int32_t heads_per_rank,
                                   int32_t head_begin, void* stream);
 
+/* Producer fusion in front of the attention path: per-head RMS norm with weight, then partial
+ * rotary embedding, in place on Q or K.  x [tokens][heads][head_dim] 16-bit (strides[2] = token and
+ * head stride in elements, multiples of 8; head_dim contiguous), weight [head_dim] in x's type,
+ * cos/sin fp32 [tokens][rotary_dim]; rotary_dim a multiple of 16, at most head_dim (0: norm only).
+ * Replaces the Triton kernel _qknorm_partial_rope_kernel / fused_qknorm_rope of
+ * anemoi/models/minimax_h3/solengine/models/minimax_h3/optimized/fusions.py:208-274. */
+int anemoi_sm100_qknorm_rope(void* x, const void* weight, const float* cos_table,
+                             const float* sin_table, int64_t tokens, int32_t heads, int32_t head_dim,
+                             int32_t rotary_dim, float eps, int32_t is_bf16, const int64_t* strides,
+                             void* stream);
+
 /* Measurement helper (no reference counterpart): throughput of the tcgen05 tensor pipe for one
  * MMA kind, with the instruction forms, shared-memory operand layout and 128x128 tile of the
  * attention kernel.  Launches 2 CTAs per SM that each issue 8*iterations MMAs; the caller times
