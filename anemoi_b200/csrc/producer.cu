@@ -18,120 +18,37 @@
 #include <stdint.h>
 
 #include "../../include/anemoi_sm100.h"
+#include "norm_rope.cuh"
 
 namespace {
 
-template <typename T>
-__device__ __forceinline__ float to_float(T v);
-template <>
-__device__ __forceinline__ float to_float<__half>(__half v) {
-  return __half2float(v);
-}
-template <>
-__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
-  return __bfloat162float(v);
-}
-template <typename T>
-__device__ __forceinline__ T from_float(float v);
-template <>
-__device__ __forceinline__ __half from_float<__half>(float v) {
-  return __float2half_rn(v);
-}
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-
-// One row (token, head) per group of D/8 consecutive lanes, 8 channels per thread; every thread
-// walks kRows rows (a block covers kRows consecutive slabs of rows) with all of their 16-byte
-// loads issued before the first use, so that enough bytes are in flight per SM.
-constexpr int kRows = 1;
-
+// One row (token, head) per group of D/8 consecutive lanes; 8 channels per thread.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) qknorm_rope_kernel(T* x, const T* weight, const float* cos_table,
                                                           const float* sin_table, int64_t rows,
                                                           int heads, int rotary_dim, float eps,
                                                           int64_t token_stride, int64_t head_stride) {
   constexpr int kLanes = D / 8;
-  constexpr int kSlab = 256 / kLanes;  // rows per block and pass
+  const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / kLanes;
   const int lane = threadIdx.x % kLanes;
-  const int64_t row0 = (int64_t)blockIdx.x * (kSlab * kRows) + threadIdx.x / kLanes;
-
-  T* ptr[kRows];
-  int64_t token[kRows];
-  bool live[kRows];
-  uint4 raw[kRows];
-#pragma unroll
-  for (int k = 0; k < kRows; ++k) {
-    const int64_t row = row0 + (int64_t)k * kSlab;
-    live[k] = row < rows;
-    // rows < 2^31 (checked by the launcher): 32-bit division
-    const uint32_t r32 = live[k] ? (uint32_t)row : 0u;
-    token[k] = r32 / (uint32_t)heads;
-    const int head = (int)(r32 - (uint32_t)token[k] * (uint32_t)heads);
-    ptr[k] = x + token[k] * token_stride + (int64_t)head * head_stride + lane * 8;
-    raw[k] = make_uint4(0, 0, 0, 0);
-    if (live[k]) raw[k] = *reinterpret_cast<const uint4*>(ptr[k]);
-  }
-  const uint4 wraw = *reinterpret_cast<const uint4*>(weight + lane * 8);
-  const T* w = reinterpret_cast<const T*>(&wraw);
-  // partner channels live half/8 lanes away (rotary_dim is a multiple of 16)
-  const int half = rotary_dim / 2;
-  const int c0 = lane * 8;
-  const bool rotary = c0 < rotary_dim;
-  const bool first = c0 < half;
-  const int partner_lane = first ? lane + half / 8 : lane - half / 8;
-
-#pragma unroll
-  for (int k = 0; k < kRows; ++k) {
-    const T* e = reinterpret_cast<const T*>(&raw[k]);
-    float v[8];
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[i] = to_float<T>(e[i]);
-      sum = __fmaf_rn(v[i], v[i], sum);
-    }
-#pragma unroll
-    for (int off = kLanes / 2; off > 0; off >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
-    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)D), eps)));
-    float n[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) n[i] = __fmul_rn(__fmul_rn(v[i], r), to_float<T>(w[i]));
-
-    float out[8];
-    float cs[8], sn[8];
-    if (rotary && live[k]) {
-      // 8 consecutive table entries of this token: two 16-byte loads each (rotary_dim % 16 == 0)
-      const float4* ct = reinterpret_cast<const float4*>(cos_table + token[k] * rotary_dim + c0);
-      const float4* st = reinterpret_cast<const float4*>(sin_table + token[k] * rotary_dim + c0);
-      *reinterpret_cast<float4*>(cs) = __ldg(ct);
-      *reinterpret_cast<float4*>(cs + 4) = __ldg(ct + 1);
-      *reinterpret_cast<float4*>(sn) = __ldg(st);
-      *reinterpret_cast<float4*>(sn + 4) = __ldg(st + 1);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      // every lane takes part in the shuffle; lanes outside the span read themselves
-      const float pn = __shfl_sync(0xffffffffu, n[i], rotary ? partner_lane : lane, kLanes);
-      out[i] = n[i];
-      if (rotary && live[k]) out[i] = __fmaf_rn(first ? -pn : pn, sn[i], __fmul_rn(n[i], cs[i]));
-    }
-    if (live[k]) {
-      uint4 packed;
-      T* o = reinterpret_cast<T*>(&packed);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = from_float<T>(out[i]);
-      *reinterpret_cast<uint4*>(ptr[k]) = packed;
-    }
-  }
+  const bool live = row < rows;
+  // rows < 2^31 (checked by the launcher): 32-bit division
+  const uint32_t r32 = live ? (uint32_t)row : 0u;
+  const int64_t token = r32 / (uint32_t)heads;
+  const int head = (int)(r32 - (uint32_t)token * (uint32_t)heads);
+  T* p = x + token * token_stride + (int64_t)head * head_stride + lane * 8;
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = *reinterpret_cast<const uint4*>(p);
+  const uint4 out = nr::norm_rope8<T, D>(raw, weight, cos_table + token * rotary_dim,
+                                         sin_table + token * rotary_dim, rotary_dim, eps, lane, live);
+  if (live) *reinterpret_cast<uint4*>(p) = out;
 }
 
 template <typename T>
 int launch(void* x, const void* weight, const float* c, const float* s, int64_t tokens, int heads, int d,
            int rotary, float eps, const int64_t* strides, cudaStream_t st) {
   const int64_t rows = tokens * heads;
-  const int64_t rows_per_block = (256 / (d / 8)) * kRows;
+  const int64_t rows_per_block = 256 / (d / 8);
   const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 0x7fffffffLL || rows > 0x7fffffffLL) return ANEMOI_SM100_ELIMIT;
   if (d == 64) {
