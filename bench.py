@@ -315,7 +315,8 @@ def run_ours(args) -> None:
             return anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
                                     quant_config=quant, calibration=calib)
         return ulysses.ulysses_anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
-                                                quant_config=quant, calibration=calib)
+                                                quant_config=quant, calibration=calib,
+                                                pipeline_groups=args.pipeline_groups)
 
     def barrier():
         if world > 1:
@@ -407,7 +408,8 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": int(out.numel() * out.element_size())},
             # 10 library kernels per attention call; with N > 1 the local heads run as pipelined
             # groups, each with its own pack and merge kernel
-            "gpu_launches": 10 if world == 1 else 12 * len(ulysses.head_groups(w["heads"] // world, 2)),
+            "gpu_launches": 10 if world == 1 else 12 * len(ulysses.head_groups(w["heads"] // world,
+                                                                               args.pipeline_groups)),
             "stage_ms": stages,
             "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
                          "achieved": achieved, "peak": mixed_peak, "unit": "TFLOP/s",
@@ -530,6 +532,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-dense", action="store_true",
                     help="skip the dense bf16 library attention timed beside the sparse layer")
+    ap.add_argument("--pipeline-groups", type=int, default=2,
+                    help="head groups whose exchange is pipelined under the attention (N > 1)")
     ap.add_argument("--sweep", action="store_true", help="run the kernel sweep instead of the benchmark")
     ap.add_argument("--sweep-heads", type=int, default=4)
     ap.add_argument("--sweep-out", default="")
