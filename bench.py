@@ -532,7 +532,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-dense", action="store_true",
                     help="skip the dense bf16 library attention timed beside the sparse layer")
-    ap.add_argument("--pipeline-groups", type=int, default=2,
+    ap.add_argument("--pipeline-groups", type=int, default=1,
                     help="head groups whose exchange is pipelined under the attention (N > 1)")
     ap.add_argument("--sweep", action="store_true", help="run the kernel sweep instead of the benchmark")
     ap.add_argument("--sweep-heads", type=int, default=4)
