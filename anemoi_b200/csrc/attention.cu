@@ -486,7 +486,14 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int QB = p.s.query_block;
-  const int tile = blockIdx.x, head = blockIdx.y;
+  const int head = blockIdx.y;
+  // launch order of the head's query blocks (longest list first) as written by the routing
+  // stage; 0 = no order given
+  int tile = blockIdx.x;
+  if (!p.dense_prefix) {
+    const int ordered = p.row_counts[((int64_t)head * p.s.video_blocks + blockIdx.x) * 4 + 3];
+    if (ordered > 0) tile = ordered - 1;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- this tile's work list ----

@@ -255,6 +255,25 @@ __global__ void __launch_bounds__(kRowThreads) emit_kernel(
   }
 }
 
+// Launch order of a head's query blocks for the attention kernel: longest list first (ties by
+// block index), written as block + 1 into the fourth entry of row_counts, slot = position.
+// The last CTAs of a launch are then the short ones, which shortens the tail during which SMs
+// run out of work.  Blocks are ranked by counting (R^2 / threads comparisons per thread).
+constexpr int kOrderMaxBlocks = 4096;
+__global__ void __launch_bounds__(1024) order_kernel(int R, int32_t* row_counts) {
+  extern __shared__ int total[];
+  const int head = blockIdx.x;
+  int32_t* rc = row_counts + (int64_t)head * R * 4;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) total[i] = rc[i * 4] + rc[i * 4 + 1] + rc[i * 4 + 2];
+  __syncthreads();
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const int mine = total[i];
+    int rank = 0;
+    for (int j = 0; j < R; ++j) rank += (total[j] > mine) || (total[j] == mine && j < i);
+    rc[rank * 4 + 3] = i + 1;
+  }
+}
+
 }  // namespace
 
 extern "C" int64_t anemoi_sm100_route_scratch_bytes(const anemoi_sm100_shape* shape) {
@@ -314,6 +333,8 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
   emit_kernel<<<dim3(R, H), kRowThreads, (size_t)((R + 15) & ~15), st>>>(
       prob, R, sc.thr, sc.eq, sc.cursor, shape->query_block / 64, rec::prefix_stages(*shape),
       prefix_phase, list_capacity, row_offset, row_counts, stage_ids);
+  // very large block counts keep the identity order (the fourth entries stay 0)
+  if (R <= kOrderMaxBlocks) order_kernel<<<H, 1024, (size_t)R * 4, st>>>(R, row_counts);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
 

@@ -120,7 +120,9 @@ int64_t anemoi_sm100_route_list_capacity(const anemoi_sm100_shape* shape, int64_
  *   n16,n8,n4    per-head budgets (FP16, INT8, NVFP4)
  *   prefix_phase -1 none, 0 nvfp4, 1 int8, 2 fp16: phase that carries the prefix stages
  *   row_offset   int32 [H][R]   start of the row's list inside the head's segment
- *   row_counts   int32 [H][R][4] stages per phase (nvfp4, int8, fp16, 0), prefix included
+ *   row_counts   int32 [H][R][4] stages per phase (nvfp4, int8, fp16), prefix included; the
+ *                fourth entry of slot i is 1 + the query block the attention kernel should run
+ *                as its i-th CTA of the head (longest list first), or 0 for "block i"
  *   stage_ids    int32 [H][capacity] lists: nvfp4 stages, int8 stages, fp16 stages;
  *                logical columns ascend inside a phase, prefix stages lead their phase
  * Ties are broken by ascending flat index row*R+col.

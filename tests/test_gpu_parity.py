@@ -127,6 +127,17 @@ def test_route_lists_bit_exact(run):
             assert np.array_equal(got, np.concatenate((nv, i8, hi))), (h, i)
 
 
+def test_launch_order_is_longest_first(run):
+    """The fourth entry of row_counts lists a head's query blocks (1-based) by descending list
+    length, ties by block index: the order in which the attention kernel launches them."""
+    case, (out, parts, oracle, geo) = run
+    cnt = parts["lists"].row_counts.cpu().numpy()
+    for h in range(cnt.shape[0]):
+        total = cnt[h, :, :3].sum(axis=1)
+        want = sorted(range(len(total)), key=lambda i: (-int(total[i]), i))
+        assert (cnt[h, :, 3] - 1).tolist() == want
+
+
 def test_attention_within_tolerance(run):
     case, (out, parts, oracle, geo) = run
     packed = parts["packed"].cpu().numpy()
