@@ -406,9 +406,10 @@ def run_ours(args) -> None:
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in (q, k, v))),
                     "d2h_bytes_per_step": int(out.numel() * out.element_size())},
-            # 10 library kernels per attention call; with N > 1 the local heads run as pipelined
-            # groups, each with its own pack and merge kernel
-            "gpu_launches": 10 if world == 1 else 12 * len(ulysses.head_groups(w["heads"] // world,
+            # 11 library kernels per attention call (v_amax, prepare, prefix attention, draft, hist,
+            # threshold, tally, emit, order, attention, assemble); with N > 1 every head group adds
+            # its pack and merge kernel
+            "gpu_launches": 11 if world == 1 else 13 * len(ulysses.head_groups(w["heads"] // world,
                                                                                args.pipeline_groups)),
             "stage_ms": stages,
             "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
