@@ -317,15 +317,14 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
       cudaMemsetAsync(sc.cursor, 0, (size_t)H * 4, st) != cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
   const unsigned short* prob = static_cast<const unsigned short*>(probability);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kBins * 4) != cudaSuccess ||
-        cudaFuncSetAttribute(emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536) !=
-            cudaSuccess)
-      return ANEMOI_SM100_ELAUNCH;
-    attr_set = true;
-  }
+  // Function attributes belong to a device: they are set at every call (two cheap host-side
+  // driver calls), so a process that routes on several GPUs, or from several host threads,
+  // never launches these kernels without the opt-in for their dynamic shared memory.
+  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBins * 4) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536) !=
+          cudaSuccess)
+    return ANEMOI_SM100_ELAUNCH;
   const int chunks = (int)max((int64_t)1, min((int64_t)16, items / 32768));
   hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, sc.hist);
   threshold_kernel<<<H, 1024, 0, st>>>(sc.hist, sc.thr, n16, n16 + n8, n16 + n8 + n4);

@@ -22,7 +22,7 @@ from . import native
 from .layout import materialize_ragged_2d_layout
 from .routing import PHASE_ORDER, resolve_phases, route_counts, video_phases
 
-_LAST_STATUS: dict = {}
+_STATUS: dict = {}
 _STAGE_EVENTS: list | None = None
 
 
@@ -180,7 +180,7 @@ def sm100_ragged_attention(
     with _Stage("prepare"):
         native.prepare(shape, q_bshd, k_bshd, v_bshd, layout.indices, layout.counts, store)
     valid_k = _valid_k(device, prefix_tokens, query_block_size, _counts_key(layout))
-    status = torch.zeros(1, dtype=torch.int32, device=device)
+    status = _status_word(device)
 
     if native_prefix:
         side.wait_stream(current)
@@ -211,7 +211,6 @@ def sm100_ragged_attention(
     with _Stage("assemble"):
         out = native.assemble(shape, prefix_out, packed, layout.inverse, lists.row_counts,
                               q_bshd.dtype)
-    _LAST_STATUS[device] = status
     if return_parts:
         return out, dict(shape=shape, store=store, prob=prob, lists=lists, packed=packed,
                          prefix_out=prefix_out, valid_k=valid_k, budgets=(n16, n8, n4),
@@ -227,16 +226,36 @@ def _counts_key(layout) -> tuple:
     return key
 
 
-def last_status(device=None) -> int:
-    """Synchronise and return the device status word of the latest call (0 = clean).
+def _status_word(device: torch.device) -> torch.Tensor:
+    """The device's sticky status word: allocated once, never cleared by a call, so the first
+    give-up of a bounded wait stays on record until ``reset_status``."""
+    device = torch.device(device)
+    word = _STATUS.get(device)
+    if word is None:
+        word = _STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
 
-    A non-zero value means a bounded wait inside the attention kernel gave up; the
-    output of that call is not valid.
+
+def last_status(device=None) -> int:
+    """Synchronise and return the device's status word (0 = clean).
+
+    A non-zero value means a bounded wait inside an attention kernel gave up in some call on
+    this device since the last ``reset_status``; that call's output is not valid.  Callers that
+    synchronise anyway (end of a request, end of a benchmark step) check it there.
     """
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    status = _LAST_STATUS.get(torch.device(device))
-    return 0 if status is None else int(status.item())
+    word = _STATUS.get(torch.device(device))
+    return 0 if word is None else int(word.item())
+
+
+def reset_status(device=None) -> None:
+    """Clear the device's status word (after a reported give-up has been handled)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = _STATUS.get(torch.device(device))
+    if word is not None:
+        word.zero_()
 
 
 def execute_ragged_attention(
@@ -285,4 +304,4 @@ def execute_ragged_attention(
     )
 
 
-__all__ = ["execute_ragged_attention", "sm100_ragged_attention", "last_status"]
+__all__ = ["execute_ragged_attention", "sm100_ragged_attention", "last_status", "reset_status"]

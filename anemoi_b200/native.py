@@ -80,6 +80,8 @@ def library() -> C.CDLL:
         "anemoi_sm100_route_static": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, P, I64, P]),
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
         "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
+        "anemoi_sm100_set_wait_limit_ns": (C.c_int, [C.c_uint64]),
+        "anemoi_sm100_wait_selftest": (C.c_int, [C.c_uint64, P, P]),
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
         "anemoi_sm100_pack_qkv": (C.c_int, [P, P, P, P, I64, I32, I32, I32, C.POINTER(I64), P]),
         "anemoi_sm100_merge_heads": (C.c_int, [P, P, I64, I32, I32, I32, P]),
@@ -106,7 +108,8 @@ EXPORTED = (
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
-    "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope",
+    "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
+    "anemoi_sm100_wait_selftest",
 )
 
 
@@ -261,6 +264,17 @@ def prefix_attention(shape: Shape, store: OperandStore, valid_k: torch.Tensor,
         C.byref(shape), C.byref(store.struct), _ptr(valid_k), _ptr(out), _ptr(status),
         _stream(dev)), "anemoi_sm100_prefix_attention")
     return out
+
+
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """Limit of every bounded wait in attention kernels launched from now on (default 2 s)."""
+    _check(library().anemoi_sm100_set_wait_limit_ns(int(limit_ns)), "anemoi_sm100_set_wait_limit_ns")
+
+
+def wait_selftest(limit_ns: int, status: torch.Tensor) -> None:
+    """Launch the one-CTA kernel whose wait must give up after ``limit_ns`` (sets ``status`` to 99)."""
+    _check(library().anemoi_sm100_wait_selftest(int(limit_ns), _ptr(status), _stream(status.device)),
+           "anemoi_sm100_wait_selftest")
 
 
 def assemble(shape: Shape, prefix_out: torch.Tensor | None, out_packed: torch.Tensor,

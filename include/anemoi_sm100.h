@@ -156,7 +156,8 @@ int anemoi_sm100_route_static(const anemoi_sm100_shape* shape, const void* proba
 /* Block-sparse mixed-precision flash attention of the video query blocks.
  *   valid_k      int32 [stages] real keys per stage
  *   out_packed   fp16 [H][R*QB][D] packed row order; rows of empty lists are not written
- *   status       int32 [1] device word, set non-zero if a bounded wait gave up
+ *   status       int32 [1] device word, set non-zero (first give-up wins, never cleared by
+ *                the library) if a bounded wait gave up; the output is then invalid
  * Replaces sm120_q{64,128}_{fp16,int8_fp16,nvfp4_fp16,nv_int8_fp16}_attention_forward
  * (sm120/bindings.cpp, sm120/q64_attention_host.cu). */
 int anemoi_sm100_attention(const anemoi_sm100_shape* shape, const anemoi_sm100_operands* ops,
@@ -164,6 +165,17 @@ int anemoi_sm100_attention(const anemoi_sm100_shape* shape, const anemoi_sm100_o
                            const int32_t* stage_ids, int64_t list_capacity,
                            const int32_t* valid_k, void* out_packed, int32_t* status,
                            void* stream);
+
+/* Limit, in nanoseconds, of every bounded wait inside the attention kernels launched after
+ * this call (default 2 s; process-wide).  No reference counterpart: the reference's kernels
+ * have no waits that another warp must satisfy. */
+int anemoi_sm100_set_wait_limit_ns(uint64_t limit_ns);
+
+/* Self-test of the give-up path of the bounded waits (no reference counterpart): one CTA
+ * waits, for at most `limit_ns` (<= 100 ms), on a barrier nothing ever arrives on, with no
+ * copy or MMA in flight; *status (device int32, zeroed by the caller) becomes 99 and the
+ * kernel returns normally. */
+int anemoi_sm100_wait_selftest(uint64_t limit_ns, int32_t* status, void* stream);
 
 /* Dense INT8-cell attention of the prefix query rows over every stage.
  *   out_prefix   fp16 [H][prefix query tiles * QB][D]

@@ -1,0 +1,83 @@
+"""GPU lifecycle checks of the sm_100a path: results do not depend on what earlier tenants left
+in recycled device memory, replays are bit-stable, and the give-up path of the kernels' bounded
+waits reports and returns (reference models: tests/test_sm120_lifecycle_cuda.py and
+tests/test_sm120_d64_cuda.py:236-258 of the reference)."""
+
+import pytest
+import torch
+
+from tests.helpers import smooth_fields
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(q, k, v, vs, prefix, ratios, drop, qb):
+    from anemoi_b200.executor import sm100_ragged_attention
+
+    return sm100_ragged_attention(
+        q, k, v, prefix_tokens=prefix, sparsity_ratio=drop, retained_nvfp4_ratio=ratios[0],
+        retained_int8_ratio=ratios[1], retained_fp16_ratio=ratios[2], video_shape=vs, layer=0,
+        query_block_size=qb, nvfp4_scales=(0.01, 0.01, 0.002))
+
+
+@pytest.mark.parametrize("cell", [(0.4, 0.4, 0.2), (0.0, 1.0, 0.0)], ids=["mixed", "int8"])
+def test_nan_poisoned_allocator_churn_and_replays(native_library, cell):
+    """Every scratch and output buffer of a call comes from the caching allocator.  Between calls
+    the freed blocks are filled with NaN; a kernel that read a byte it had not written, or left
+    an output row unwritten, would show it.  The case drops 97 % of the block pairs so that some
+    query blocks have empty lists (their rows must be +0), and is replayed 128 times."""
+    from anemoi_b200.executor import last_status
+
+    vs, prefix, qb = (4, 16, 16), 0, 64
+    q, k, v = (t.cuda() for t in smooth_fields(*vs, 2, 128, prefix, seed=5, outliers=(17, 93),
+                                               dtype=torch.bfloat16))
+    first = _call(q, k, v, vs, prefix, cell, 0.97, qb).clone()
+    assert torch.isfinite(first).all()
+    assert (first[0].view(torch.int16) == 0).all(dim=-1).any(), "expected some empty query blocks"
+    for rep in range(128):
+        if rep % 8 == 0:
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            poison = [torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+                      for n in (1 << 22, 1 << 20, 3 << 18, 1 << 16, 1 << 12)]
+            del poison
+        out = _call(q, k, v, vs, prefix, cell, 0.97, qb)
+        assert torch.equal(out, first), rep
+    assert last_status() == 0
+
+
+def test_bounded_wait_gives_up_and_the_next_call_is_clean(native_library):
+    """A wait that nothing can satisfy (a barrier nobody arrives on, no copy or MMA in flight)
+    returns after its limit with the status word set; the context stays usable and the next
+    attention call is clean."""
+    from anemoi_b200 import native
+    from anemoi_b200.executor import last_status
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    native.wait_selftest(200_000, status)          # 0.2 ms
+    torch.cuda.synchronize()
+    assert int(status.item()) == 99
+    vs = (2, 10, 14)
+    q, k, v = (t.cuda() for t in smooth_fields(*vs, 2, 128, 0, seed=2, dtype=torch.bfloat16))
+    out = _call(q, k, v, vs, 0, (0.4, 0.4, 0.2), 0.5, 64)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    assert last_status() == 0
+
+
+def test_route_runs_on_every_visible_device(native_library):
+    """Function attributes are per device: routing on a second GPU of the same process must
+    not fail its launch (one GPU: the loop runs once)."""
+    from anemoi_b200.executor import last_status
+
+    vs = (2, 10, 14)
+    q, k, v = smooth_fields(*vs, 2, 128, 0, seed=2, dtype=torch.bfloat16)
+    outs = []
+    for dev in range(min(torch.cuda.device_count(), 2)):
+        with torch.cuda.device(dev):
+            out = _call(q.cuda(dev), k.cuda(dev), v.cuda(dev), vs, 0, (0.0, 1.0, 0.0), 0.5, 64)
+            torch.cuda.synchronize(dev)
+            assert last_status(torch.device("cuda", dev)) == 0
+            outs.append(out.cpu())
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])

@@ -19,6 +19,25 @@ CASES = [
     ("q64_d128_nv", (2, 10, 14), 33, 2, 128, 64, torch.bfloat16, (1.0, 0.0, 0.0), 0.6, 0.0, "nvfp4", "fp16"),
     ("q128_d64_f16", (2, 12, 12), 64, 2, 64, 128, torch.float16, (0.0, 0.0, 1.0), 0.5, 0.0, "fp16", "fp16"),
     ("q128_nv_f16_pint8", (2, 12, 12), 40, 2, 128, 128, torch.bfloat16, (0.5, 0.0, 0.5), 0.5, 0.25, "int8", "fp16"),
+    # the NVFP4+INT8 cell (no FP16 phase), prefixed and visual-only, both query blocks and head dims
+    ("q128_nv_i8_prefix", (3, 12, 20), 70, 2, 128, 128, torch.bfloat16, (0.5, 0.5, 0.0), 0.7, 0.0, "int8", "int8"),
+    ("q64_d64_nv_i8", (2, 10, 14), 0, 2, 64, 64, torch.float16, (0.5, 0.5, 0.0), 0.5, 0.0, "int8", "int8"),
+    # the NVFP4 phase holds nothing but the prefix stages
+    ("q128_i8_prefix_nvfp4", (2, 12, 12), 40, 2, 128, 128, torch.bfloat16, (0.0, 1.0, 0.0), 0.5, 0.0, "nvfp4", "int8"),
+    # Q128 blocks of 64 real keys: every second stage of a block is fully masked (valid_k == 0)
+    ("q128_half_blocks", (5, 8, 8), 20, 2, 128, 128, torch.bfloat16, (0.3, 0.4, 0.3), 0.4, 0.0, "int8", "int8"),
+    # rest of the cell x head-dim x query-block matrix
+    ("q128_d64_nv", (2, 12, 12), 0, 2, 64, 128, torch.float16, (1.0, 0.0, 0.0), 0.5, 0.0, "int8", "int8"),
+    ("q64_d128_i8_prefix", (2, 10, 14), 50, 2, 128, 64, torch.bfloat16, (0.0, 1.0, 0.0), 0.6, 0.0, "int8", "int8"),
+    ("q64_d128_f16", (2, 10, 14), 0, 2, 128, 64, torch.bfloat16, (0.0, 0.0, 1.0), 0.6, 0.0, "int8", "int8"),
+    ("q64_d64_nv_f16_prefix", (2, 10, 14), 30, 2, 64, 64, torch.float16, (0.5, 0.0, 0.5), 0.5, 0.0, "fp16", "fp16"),
+    ("q64_d64_i8_f16", (2, 10, 14), 0, 2, 64, 64, torch.float16, (0.0, 0.5, 0.5), 0.5, 0.5, "int8", "int8"),
+    ("q64_d128_mixed_prefix", (2, 10, 14), 90, 2, 128, 64, torch.bfloat16, (0.4, 0.4, 0.2), 0.5, 0.0, "int8", "int8"),
+    ("q128_d64_mixed", (3, 12, 20), 0, 2, 64, 128, torch.float16, (0.4, 0.4, 0.2), 0.6, 0.0, "int8", "int8"),
+    ("q128_d64_i8_prefix", (2, 12, 12), 130, 2, 64, 128, torch.float16, (0.0, 1.0, 0.0), 0.5, 0.0, "int8", "int8"),
+    # 99 % of the block pairs dropped: the global budget of a head (3 of 256 pairs) leaves most
+    # query blocks with an empty list
+    ("q64_empty_rows", (4, 16, 16), 0, 2, 64, 64, torch.float16, (0.0, 0.5, 0.5), 0.99, 0.0, "int8", "int8"),
 ]
 
 
@@ -153,6 +172,27 @@ def test_attention_within_tolerance(run):
             ma, cos, _ = compare_metrics(packed[h, rows], want[rows])
             worst = (max(worst[0], ma), min(worst[1], cos))
     assert worst[0] <= 2e-2 and worst[1] >= 0.999, worst
+
+
+def test_empty_lists_give_positive_zero(run):
+    """Query blocks whose three counts are all zero are never touched by the attention kernel;
+    the assembly writes +0 for their tokens (reference: csrc/attention/cuda/sm89/
+    output_assembly.cu:272-291, tests/test_sm120_d64_cuda.py:236-258): no NaN, sign bit clear."""
+    case, (out, parts, oracle, geo) = run
+    cnt = parts["lists"].row_counts.cpu().numpy()
+    QB = parts["shape"].query_block
+    prefix = case[2]
+    bits = out[0].view(torch.int16).cpu().numpy()
+    empty_blocks = 0
+    for h in range(cnt.shape[0]):
+        for i in range(cnt.shape[1]):
+            if cnt[h, i, :3].sum() != 0:
+                continue
+            empty_blocks += 1
+            tokens = geo.indices[i * QB : i * QB + int(geo.counts[i])]
+            assert (bits[prefix + tokens, h] == 0).all(), (h, i)
+    if case[0] == "q64_empty_rows":
+        assert empty_blocks >= 10
 
 
 def test_output_within_tolerance(run):
