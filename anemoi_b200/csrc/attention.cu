@@ -1,33 +1,34 @@
 // Block-sparse mixed-precision flash attention for sm_100a.
 //
-// One CTA (640 threads, one per SM) owns one query tile: QB rows of one head, padded to the
-// 128-row MMA shape.  It walks the tile's ragged list of 64-key stages in the order
-// NVFP4 -> INT8 -> FP16.  Stage g runs in pipeline g % 3 (its own score buffer S in tensor
-// memory and its own probability tile P in shared memory) and accumulates into output
-// accumulator g % 2, so three stages are in flight: while one pipeline does its exponentials,
-// the tensor core computes QK^T and PV for the others.  The running row maximum is still ONE
-// sequence over all stages (each pipeline hands its new maximum to the next through shared
-// memory), so every probability is quantised against exactly the maximum a strictly
-// sequential walk would use; only the fp32 accumulation is split over two accumulators and
-// merged in the epilogue.
+// One CTA owns one query tile (QB rows of one head, padded to the 128-row MMA
+// shape) and walks that tile's ragged list of 64-key stages in the order
+// NVFP4 -> INT8 -> FP16 with one online-softmax state.
 //
-// Warp roles (five warpgroups, registers moved between them with setmaxnreg):
-//   warps 0-11  softmax of pipelines 0..2 (four warps each): thread = query row = TMEM lane;
-//               loads the row's 64 scores, releases S, finds the maximum, computes
-//               P = 2^(s*scale - m), its sum, converts P to the cell's operand format
-//   warps 12-15 correction: rescale an accumulator when the maximum moved since the stage
-//               that last touched it (and convert it between the value domains of the
-//               phases), off the softmax warps' path
-//   warp 16     loader: 1-D bulk copies (TMA engine) of the Q records and of the key and value
-//               parts of each stage record into two rings of shared-memory units
-//   warps 17-19 MMA of pipelines 0..2: one lane each issues tcgen05.mma (QK^T into S, PV into
-//               O) and tcgen05.commit to mbarriers
-// TMEM (512 columns): O accumulators at [0,D) and [128,128+D); S of pipeline p at
-// [256+64p, +64); scale factors of the NVFP4 phase at [448,512).
+// Warp roles (256 threads = two warpgroups; the second one gives most of its registers to the
+// first with setmaxnreg, so a softmax thread may use 192 registers at two CTAs per SM):
+//   warps 0-3  softmax: warp w owns TMEM lanes 32*w.. (query rows); one thread per row holds
+//              the row's 64 scores of a stage in registers (few threads with long unrolled
+//              instruction streams: the per-stage fixed cost is paid once per row)
+//   warp 4     loader: one lane issues 1-D bulk copies (TMA engine) of the Q record of
+//              each phase and of one K|V record per stage into a ring of shared-memory
+//              slots, completion counted on mbarriers
+//   warp 5     MMA: allocates TMEM; one lane issues tcgen05.mma
+//                S[128x64]  = Q K^T   kind::mxf4nvf4 / kind::i8 / kind::f16
+//                O[128xD]  += P V     kind::mxf4nvf4 / kind::f8f6f4 / kind::f16
+//              and tcgen05.commit to mbarriers
+//   warps 6-7  idle (they complete the second warpgroup)
+// TMEM columns: S0 [0,64), O [64,64+D), and [192,256) holds the NVFP4 scale factors in the
+// NVFP4 phase and a second score buffer S1 in the INT8 / FP16 phases (QK of stage g+1 runs
+// while the softmax threads still read the scores of stage g).
+// O stays in TMEM across all stages; it is rescaled (read-modify-write by the
+// softmax threads) only when some row's running maximum moved, and at a phase
+// change, where it is also converted between the phases' value domains.  P is
+// double-buffered in shared memory for the 4- and 8-bit cells, so the softmax
+// threads only wait for the previous PV when they have to rescale O.
 //
 // Numerics follow the reference's phases
-// (csrc/attention/cuda/sm120/q64_attention_phase_composer.inl:1-146, 506-932, 934-1331;
-// primitives/qattn/attn_utils.cuh:363-389, 470-625):
+// (csrc/attention/cuda/sm120/q64_attention_phase_composer.inl:1-146, 506-932,
+// 934-1331; primitives/qattn/attn_utils.cuh:363-389, 470-625):
 //   base-2 online softmax, sigma = log2(e)/sqrt(D), m0 = -5e6, keys >= valid_k masked,
 //   denominator accumulated from the unquantised P,
 //   NVFP4: score scale sigma*q_gs*k_gs, P -> e2m1(6P) with a constant 448 block scale,
@@ -35,8 +36,8 @@
 //   INT8 : exact s32 scores, scale sigma*q_scale*k_scale[stage], P -> e4m3(P*2^8.807),
 //          O_true[c] = O[c] * v_scale[c] * 2^-8.807
 //   FP16 : P -> f16
-// Accumulation is fp32 in TMEM (the reference accumulates a stage in fp16 for the INT8 and
-// FP16 cells).
+// Accumulation is fp32 in TMEM (the reference accumulates a stage in fp16 for the
+// INT8 and FP16 cells).
 #include <climits>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
@@ -50,46 +51,24 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kPipes = 3;
-constexpr int kThreads = 640;
-// setmaxnreg moves registers inside the CTA's own pool, which is what the CTA was launched
-// with: 640 threads x 96 registers (the most the launch bound allows).  An increase that the
-// decreases of the same CTA cannot cover would wait forever.
-constexpr int kLaunchRegs = 96;
-constexpr int kSoftmaxRegs = 128;
-constexpr int kCorrectionRegs = 48;
-constexpr int kOtherRegs = 48;
-static_assert(kPipes * 128 * kSoftmaxRegs + 128 * kCorrectionRegs + 128 * kOtherRegs <=
-                  kThreads * kLaunchRegs,
-              "register budget of the warpgroups exceeds the CTA's pool");
-constexpr int kSoftmaxThreads = kPipes * 128;
-constexpr int kCorrectionWarp0 = 12;
-constexpr int kLoaderWarp = 16;
-constexpr int kMmaWarp0 = 17;
-constexpr int kTmemCols = 512;
-constexpr int kColO = 0;       // + 128 * accumulator
-constexpr int kColS = 256;     // + 64 * pipeline
-constexpr int kColSf = 448;    // + 20 * pipeline: K scales (8), V scales (4), Q scales (8)
-constexpr int kSfbK = 0, kSfbV = 8, kSfaQ = 12;
-constexpr int kColSfaP = 508;  // constant 448 block scale of P, shared by the pipelines
-constexpr int kMaxUnits = 2 * kPipes;
-constexpr int kPBytes = 16384;      // P tile of one pipeline (128 x 64 f16 is the largest)
-constexpr int kSmemLimit = 232448;  // dynamic shared memory a CTA may opt into
+constexpr int kThreads = 256;         // two warpgroups: softmax | loader, MMA and two idle warps
+constexpr int kSoftmaxRegs = 192;     // 128 * 192 + 128 * 64 == 256 * 128 (two CTAs per SM)
+constexpr int kOtherRegs = 64;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kLoaderWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kTmemCols = 256;
+constexpr int kColS = 0;
+constexpr int kColS1 = 192;  // second score buffer; aliases the scale-factor columns
+constexpr int kColO = 64;
+constexpr int kColSfaQ = 192;  // 2 k-steps x 4 columns
+constexpr int kColSfbK = 200;  // 2 k-steps x 4 columns
+constexpr int kColSfaP = 208;
+constexpr int kColSfbV = 212;
+constexpr int kMaxSlots = 8;
 constexpr float kFp8Offset = 8.807f;
-constexpr float kFp8OffsetInv = 0.0022326917f;  // 2^-8.807
 
 enum Cell : int { kNv = 0, kI8 = 1, kF16 = 2 };
-
-#ifdef ATTN_PROFILE
-// Debug build only: cycles spent per wait site, summed over all CTAs (lane 0 of each warp).
-__device__ unsigned long long g_prof[64];
-#define PROF_BEGIN() const long long prof_t0_ = clock64()
-#define PROF_END(i) \
-  if ((threadIdx.x & 31) == 0) atomicAdd(&g_prof[i], (unsigned long long)(clock64() - prof_t0_))
-#else
-#define PROF_BEGIN()
-#define PROF_END(i)
-#endif
 
 struct AttnParams {
   anemoi_sm100_shape s;
@@ -106,53 +85,31 @@ struct AttnParams {
   int stages;        // 64-key stages per head
   int q_tiles_int8;  // records per head in q_int8 (R + prefix query tiles)
   int out_rows;      // rows per head in `out`
-  int q_off[3];      // byte offsets of the three Q records in shared memory
-  int p_off;         // three P tiles
-  int k_off, k_unit, k_units;  // ring of key units
-  int v_off, v_unit, v_units;  // ring of value units
-  int misc_off;      // Scratch, then Barriers
+  int ring_bytes;    // key/value ring; re-partitioned into equal slots at every phase
+  int q_region;      // bytes
+  int p_region;      // bytes
 };
 
 struct Barriers {
-  uint64_t k_full[kMaxUnits], k_free[kMaxUnits];  // key part of a stage landed / QK complete
-  uint64_t v_full[kMaxUnits], v_free[kMaxUnits];  // value part landed / PV complete
-  uint64_t q_full;
-  uint64_t s_full[kPipes];   // scores of the pipeline's stage ready
-  uint64_t s_free[kPipes];   // ... and read into registers by its four softmax warps
-  uint64_t p_full[kPipes];   // P written
-  uint64_t p_free[kPipes];   // ... and read by its PV
-  uint64_t o_ok[kPipes];     // the stage's accumulator is in the state its PV may add onto
-  uint64_t pv_done[2];       // PV into the accumulator complete
-  uint64_t m_ready[kPipes][4];  // new running maximum published, per warp
-  uint64_t c_req[kPipes][4];    // rescale request to the correction warp of the same rows
-  uint64_t c_ack[kPipes][4];    // ... read by it
-  uint64_t all_done;
+  uint64_t kv_full[kMaxSlots];
+  uint64_t kv_free[kMaxSlots];
+  uint64_t q_full, q_free;
+  uint64_t s_full[2];  // scores ready, per score buffer
+  uint64_t s_free;     // scores read by the softmax warps (NVFP4 phase: single buffer)
+  uint64_t all_done;  // every MMA of the tile complete (epilogue)
+  // Two P barriers used alternately: a warp that skips the wait for the previous PV may run one stage
+  // ahead, and its arrival must not be counted into the previous stage's phase.
+  uint64_t p_full[2];
   WaitContext wc;
   uint32_t tmem_base;
 };
-
-struct Scratch {
-  float m[kPipes][128];      // running maximum after the pipeline's latest stage
-  float alpha[kPipes][128];  // factor for the accumulator of the pipeline's current stage
-  float fin_m[kPipes][128];  // final maximum / partial denominator of each pipeline
-  float fin_d[kPipes][128];
-  float colf[3][128];        // per-channel domain change NVFP4->INT8, NVFP4->FP16, INT8->FP16
-  float dom_i8[128];         // v_scale[c] * 2^-8.807
-  int flag[kPipes][4];       // request word: bit 0 rescale, cells in bits 4.. (from), 8.. (to)
-};
-
-struct Plan {
-  int c0, c01, n;  // stages: [0,c0) NVFP4, [c0,c01) INT8, [c01,n) FP16
-};
-__device__ __forceinline__ int cell_of(const Plan& pl, int g) {
-  return g < pl.c0 ? kNv : (g < pl.c01 ? kI8 : kF16);
-}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -175,6 +132,7 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
+
 __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
   float2 d;
   asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
@@ -190,99 +148,61 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t v) {
                : "memory");
 }
 
-
-// bytes of the key part / value part of a stage record, and where they sit in the record
 template <int D>
-__device__ __host__ __forceinline__ int k_bytes(int cell) {
-  return cell == kNv ? 32 * D + (D / 64) * 512 : (cell == kI8 ? 64 * D : 128 * D);
-}
-template <int D>
-__device__ __host__ __forceinline__ int v_bytes(int cell) {
-  return cell == kNv ? 32 * D + 512 : (cell == kI8 ? 64 * D : 128 * D);
-}
-template <int D>
-__device__ __forceinline__ int rec_bytes(int cell) {
-  return cell == kNv ? (int)rec::kv_nvfp4_bytes(D)
-                     : (cell == kI8 ? (int)rec::kv_int8_bytes(D) : (int)rec::kv_fp16_bytes(D));
-}
+struct CellInfo {
+  // bytes per stage record and per Q record, chunk counts (16-byte chunks per row)
+  __device__ static int kv_bytes(int cell) {
+    return cell == kNv ? (int)rec::kv_nvfp4_bytes(D)
+                       : (cell == kI8 ? (int)rec::kv_int8_bytes(D) : (int)rec::kv_fp16_bytes(D));
+  }
+  __device__ static int q_bytes(int cell, int qb) {
+    return cell == kNv ? (int)rec::q_nvfp4_bytes(qb, D)
+                       : (cell == kI8 ? (int)rec::q_int8_bytes(qb, D) : (int)rec::q_fp16_bytes(qb, D));
+  }
+};
 
 // ------------------------------------------------------------------------------------------
 // softmax side
 // ------------------------------------------------------------------------------------------
-// 64 scores of one stage: s32 -> f32 for the INT8 cell, masking of the padded keys, row maximum.
-__device__ __forceinline__ float stage_max(uint32_t (&r)[64], bool is_i8, int valid) {
-  if (is_i8) {
-    // as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, so the conversion is an
-    // integer add and a float subtract (no conversion instruction)
-    const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
+struct RowState {
+  float m, d;
+};
+
+// O[row][c] *= alpha (* colf[c] when kColf) for all D columns of the thread's row, 64 columns
+// (two TMEM loads in flight) per step.
+template <int D, bool kColf>
+__device__ __forceinline__ void rescale_o(uint32_t tmem_row, float alpha, const float* colf) {
+  const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll 1
+  for (int c0 = 0; c0 < D; c0 += 64) {
+    uint32_t r[64];
+    tmem_ld32(tmem_row + kColO + c0, *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_ld32(tmem_row + kColO + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
+    tmem_wait_ld();
 #pragma unroll
     for (int j = 0; j < 64; j += 2) {
-      const float2 v = fadd2(make_float2(__int_as_float((int)r[j] + 0x4B400000),
-                                         __int_as_float((int)r[j + 1] + 0x4B400000)),
-                             magic2);
+      float2 v = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), alpha2);
+      if (kColf) v = fmul2(v, *reinterpret_cast<const float2*>(colf + c0 + j));
       r[j] = __float_as_uint(v.x);
       r[j + 1] = __float_as_uint(v.y);
     }
+    tmem_st32(tmem_row + kColO + c0, *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_st32(tmem_row + kColO + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
   }
-  if (valid < 64) {
-    // ragged blocks usually lose only a few keys: the common case touches the last 8 columns
-    if (valid >= 56) {
-#pragma unroll
-      for (int j = 56; j < 64; ++j) r[j] = j < valid ? r[j] : 0xff800000u;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 64; ++j) r[j] = j < valid ? r[j] : 0xff800000u;
-    }
-  }
-#define S_(j) __uint_as_float(r[(j)])
-  float m0 = max3(S_(0), S_(1), S_(2)), m1 = max3(S_(3), S_(4), S_(5));
-  float m2 = max3(S_(6), S_(7), S_(8)), m3 = max3(S_(9), S_(10), S_(11));
-#pragma unroll
-  for (int j = 12; j < 60; j += 8) {
-    m0 = max3(m0, S_(j), S_(j + 1));
-    m1 = max3(m1, S_(j + 2), S_(j + 3));
-    m2 = max3(m2, S_(j + 4), S_(j + 5));
-    m3 = max3(m3, S_(j + 6), S_(j + 7));
-  }
-  m0 = max3(m0, S_(60), S_(61));
-  m1 = max3(m1, S_(62), S_(63));
-#undef S_
-  return fmaxf(max3(m0, m1, m2), m3);
+  tmem_wait_st();
 }
 
-// P = 2^(s*scale + bias) in place for 64 scores; returns their sum.
-__device__ __forceinline__ float stage_exp(uint32_t (&r)[64], float scale, float bias) {
-  const float2 scale2 = make_float2(scale, scale);
-  const float2 bias2 = make_float2(bias, bias);
-  float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
-#pragma unroll
-  for (int j = 0; j < 64; j += 4) {
-    const float2 a0 = ffma2(
-        make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), scale2, bias2);
-    const float2 a1 = ffma2(
-        make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), scale2, bias2);
-    const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x), e3 = ex2(a1.y);
-    r[j] = __float_as_uint(e0);
-    r[j + 1] = __float_as_uint(e1);
-    r[j + 2] = __float_as_uint(e2);
-    r[j + 3] = __float_as_uint(e3);
-    acc0 = fadd2(acc0, make_float2(e0, e1));
-    acc1 = fadd2(acc1, make_float2(e2, e3));
-  }
-  return (acc0.x + acc0.y) + (acc1.x + acc1.y);
-}
-
-// Writes 64 probabilities of the thread's row into a K-major P tile (128 rows x 64 keys).
+// Writes the thread's 64 probabilities (one query row of the stage) into the K-major P tile
+// in shared memory.
 template <int CELL>
-__device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const uint32_t (&r)[64]) {
-#define P_(j) __uint_as_float(r[(j)])
+__device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const float (&p)[64]) {
   if (CELL == kF16) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       uint4 v;
       __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(P_(j * 8 + 2 * i), P_(j * 8 + 2 * i + 1));
+      for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j * 8 + 2 * i], p[j * 8 + 2 * i + 1]);
       *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 8)) = v;
     }
   } else if (CELL == kI8) {
@@ -292,7 +212,7 @@ __device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const uint32_t
       uint16_t* h = reinterpret_cast<uint16_t*>(&v);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        h[i] = __nv_cvt_float2_to_fp8x2(make_float2(P_(j * 16 + 2 * i), P_(j * 16 + 2 * i + 1)),
+        h[i] = __nv_cvt_float2_to_fp8x2(make_float2(p[j * 16 + 2 * i], p[j * 16 + 2 * i + 1]),
                                         __NV_SATFINITE, __NV_E4M3);
       *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 4)) = v;
     }
@@ -303,138 +223,220 @@ __device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const uint32_t
       uint8_t* h = reinterpret_cast<uint8_t*>(&v);
 #pragma unroll
       for (int i = 0; i < 16; ++i)
-        h[i] = __nv_cvt_float2_to_fp4x2(make_float2(P_(j * 32 + 2 * i), P_(j * 32 + 2 * i + 1)),
-                                        __NV_E2M1, cudaRoundNearest);  // r already holds 6 P
+        h[i] = __nv_cvt_float2_to_fp4x2(make_float2(p[j * 32 + 2 * i], p[j * 32 + 2 * i + 1]),
+                                        __NV_E2M1, cudaRoundNearest);  // p already holds 6 P
       *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, 2)) = v;
     }
   }
-#undef P_
 }
 
-// O[row][c] *= alpha (* colf[c]) for all D columns of the thread's row.
+// Bytes of one P tile (128 rows x 64 keys) per cell, and which of the two buffers stage g uses.
+__device__ __forceinline__ int p_tile_bytes(int cell) {
+  return cell == kNv ? 128 * 32 : (cell == kI8 ? 128 * 64 : 128 * 128);
+}
+__device__ __forceinline__ int p_buffer(int cell, int g) { return cell == kF16 ? 0 : (g & 1); }
+// Score buffer of stage g: the NVFP4 phase has a single one (the other holds its scale factors).
+__device__ __forceinline__ int s_buffer(int cell, int g) { return cell == kNv ? 0 : (g & 1); }
+__device__ __forceinline__ uint32_t s_column(int sb) { return sb ? kColS1 : kColS; }
+
+// One stage of one phase for the thread's row.  A single copy of this code serves the three
+// cells (the cell is a run-time value): the kernel's hot code has to stay well inside the
+// instruction cache, and three unrolled copies did not.
 template <int D>
-__device__ __forceinline__ void rescale_o(uint32_t tmem_o_row, float alpha, const float* colf) {
-  const float2 alpha2 = make_float2(alpha, alpha);
-#pragma unroll 1
-  for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t r[32];
-    tmem_ld32(tmem_o_row + c0, r);
+__device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
+                                              const float* colf, uint32_t tmem_row, int row,
+                                              int cell, int g, bool phase_first,
+                                              float score_scale, int valid, bool live_warp, int sb,
+                                              uint32_t s_parity, uint64_t* prev_pv_bar,
+                                              uint32_t prev_pv_parity, RowState& st) {
+  wait(&b->wc, &b->s_full[sb], s_parity, 10 + cell);
+  tc_fence_after_sync();
+  // Barrier arrivals are one per warp (lane 0 after a warp sync).
+  const bool lead = (row & 31) == 0;
+  if (!live_warp) {
+    // padding rows of a 64-row tile: keep the barrier protocol, skip the math
+    if (lead) {
+      if (cell == kNv) mbar_arrive(&b->s_free);
+      mbar_arrive(&b->p_full[g & 1]);
+    }
+    return;
+  }
+  float s[64];
+  {
+    uint32_t r[64];
+    tmem_ld32(tmem_row + s_column(sb), *reinterpret_cast<uint32_t(*)[32]>(r));
+    tmem_ld32(tmem_row + s_column(sb) + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
     tmem_wait_ld();
-    if (colf != nullptr) {
+    if (cell == kNv) {
+      // Only the NVFP4 phase has a single score buffer, whose release the MMA warp must see
+      // before the next QK.  With two buffers, QK of stage g+2 is issued after the MMA warp has
+      // waited for P of stage g, which every softmax thread writes after this load.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lead) mbar_arrive(&b->s_free);
+    }
+    if (cell == kI8) {
+      // Scores are s32; as_float(i + 0x4B400000) == 12582912 + i exactly for |i| < 2^22, so
+      // the conversion is an integer add and a float subtract (no conversion instruction).
+      const float2 magic2 = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        float2 v = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), alpha2);
-        v = fmul2(v, *reinterpret_cast<const float2*>(colf + c0 + j));
-        r[j] = __float_as_uint(v.x);
-        r[j + 1] = __float_as_uint(v.y);
+      for (int j = 0; j < 64; j += 2) {
+        const float2 v = fadd2(make_float2(__int_as_float((int)r[j] + 0x4B400000),
+                                           __int_as_float((int)r[j + 1] + 0x4B400000)),
+                               magic2);
+        s[j] = v.x;
+        s[j + 1] = v.y;
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float2 v = fmul2(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), alpha2);
-        r[j] = __float_as_uint(v.x);
-        r[j + 1] = __float_as_uint(v.y);
+      for (int j = 0; j < 64; ++j) s[j] = __uint_as_float(r[j]);
+    }
+  }
+  if (valid < 64) {
+    // ragged blocks usually lose only a few keys: the common case touches the last 8 columns
+    if (valid >= 56) {
+#pragma unroll
+      for (int j = 56; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) s[j] = j < valid ? s[j] : -INFINITY;
+    }
+  }
+  float mx;
+  {
+    float m0 = max3(s[0], s[1], s[2]), m1 = max3(s[3], s[4], s[5]);
+    float m2 = max3(s[6], s[7], s[8]), m3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+    for (int j = 12; j < 60; j += 8) {
+      m0 = max3(m0, s[j], s[j + 1]);
+      m1 = max3(m1, s[j + 2], s[j + 3]);
+      m2 = max3(m2, s[j + 4], s[j + 5]);
+      m3 = max3(m3, s[j + 6], s[j + 7]);
+    }
+    m0 = max3(m0, s[60], s[61]);
+    m1 = max3(m1, s[62], s[63]);
+    mx = fmaxf(max3(m0, m1, m2), m3);
+  }
+
+  const float m_new = fmaxf(st.m, mx * score_scale);
+  const float alpha = ex2(st.m - m_new);
+  // exponent = s * scale + bias; the NVFP4 cell produces 6 P directly (e2m1 input range),
+  // the INT8 cell P * 2^8.807 (e4m3 input range); the sums are scaled back.
+  const float bias = cell == kI8 ? kFp8Offset - m_new
+                                 : (cell == kNv ? 2.5849625007f - m_new : -m_new);
+  const float sum_scale = cell == kI8 ? 0.0022326917f : (cell == kNv ? 0.16666667f : 1.0f);
+  const float2 scale2 = make_float2(score_scale, score_scale);
+  const float2 bias2 = make_float2(bias, bias);
+  float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int j = 0; j < 64; j += 4) {
+    const float2 a0 = ffma2(make_float2(s[j], s[j + 1]), scale2, bias2);
+    const float2 a1 = ffma2(make_float2(s[j + 2], s[j + 3]), scale2, bias2);
+    const float e0 = ex2(a0.x), e1 = ex2(a0.y), e2 = ex2(a1.x), e3 = ex2(a1.y);
+    s[j] = e0;
+    s[j + 1] = e1;
+    s[j + 2] = e2;
+    s[j + 3] = e3;
+    acc0 = fadd2(acc0, make_float2(e0, e1));
+    acc1 = fadd2(acc1, make_float2(e2, e3));
+  }
+  const float sum = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * sum_scale;
+  st.d = st.d * alpha + sum;
+  st.m = m_new;
+
+  if (g > 0) {
+    const bool need = phase_first || __any_sync(0xffffffffu, alpha != 1.0f);
+    // O may only be touched once the previous PV is complete.  The single FP16 P
+    // buffer also needs that; the double-buffered 4/8-bit P tiles are free as soon as
+    // this stage's scores arrived (QK of stage g is issued after PV of stage g-2).
+    if (need || cell == kF16) {
+      // the previous stage's PV signals the release of its key/value slot
+      wait(&b->wc, prev_pv_bar, prev_pv_parity, 20 + cell);
+      tc_fence_after_sync();
+    }
+    if (need) {
+      if (phase_first) {
+        rescale_o<D, true>(tmem_row, alpha, colf);
+      } else {
+        rescale_o<D, false>(tmem_row, alpha, nullptr);
       }
     }
-    tmem_st32(tmem_o_row + c0, r);
   }
-  tmem_wait_st();
+  uint8_t* p_tile = p_smem + p_buffer(cell, g) * p_tile_bytes(cell);
+  if (cell == kNv) {
+    write_p<kNv>(p_tile, row, s);
+  } else if (cell == kI8) {
+    write_p<kI8>(p_tile, row, s);
+  } else {
+    write_p<kF16>(p_tile, row, s);
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lead) mbar_arrive(&b->p_full[g & 1]);
 }
 
 // ------------------------------------------------------------------------------------------
 // MMA side
 // ------------------------------------------------------------------------------------------
-// S[128 x 64] = Q K^T for the key unit at `k_addr`; `tmem_sf` = the pipeline's scale columns.
 template <int D>
-__device__ __forceinline__ void issue_qk(int cell, uint32_t tmem_s, uint32_t tmem_sf,
-                                         uint32_t q_addr, uint32_t k_addr) {
+__device__ __forceinline__ void issue_qk(int cell, uint32_t tmem_s, uint32_t tmem, uint32_t q_addr,
+                                         uint32_t k_addr, uint32_t kv_slot_addr, uint32_t issue) {
   if (cell == kF16) {
     constexpr uint32_t chunks = D / 8;
     const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 16; ++k)
       mma_f16_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
-                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+                 smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else if (cell == kI8) {
     constexpr uint32_t chunks = D / 16;
     const uint32_t idesc = instr_desc(kFmtS8, kFmtS8, kAccS32, 128, 64, 0, 0);
 #pragma unroll
     for (int k = 0; k < D / 32; ++k)
       mma_i8_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
-                smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0);
+                smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0, issue);
   } else {
     constexpr uint32_t chunks = D / 32;
     const uint32_t idesc = instr_desc_nvf4(128, 64);
-    const uint32_t ksf = k_addr + 32 * D;  // scale blocks follow the codes in the unit
+    const uint32_t ksf = kv_slot_addr + rec::kv_nvfp4_ksf_offset(D);
 #pragma unroll
     for (int k = 0; k < D / 64; ++k)
-      tmem_cp_32x128b_warpx4(tmem_sf + kSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128));
+      tmem_cp_32x128b_warpx4(tmem + kColSfbK + 4 * k, smem_desc(ksf + 512 * k, 128, 128), issue);
 #pragma unroll
     for (int k = 0; k < D / 64; ++k)
       mma_nvf4_ss(tmem_s, smem_desc(q_addr + k * 256, 128, chunks * 128),
                   smem_desc(k_addr + k * 256, 128, chunks * 128), idesc, k > 0,
-                  tmem_sf + kSfaQ + 4 * k, tmem_sf + kSfbK + 4 * k);
+                  tmem + kColSfaQ + 4 * k, tmem + kColSfbK + 4 * k, issue);
   }
 }
 
-// O[128 x D] (+)= P[128 x 64] V for the value unit at `v_addr`.
 template <int D>
-__device__ __forceinline__ void issue_pv(int cell, uint32_t tmem_o, uint32_t tmem_sf,
-                                         uint32_t tmem_sfa_p, uint32_t p_addr, uint32_t v_addr,
-                                         uint32_t accumulate) {
+__device__ __forceinline__ void issue_pv(int cell, uint32_t tmem, uint32_t p_addr,
+                                         uint32_t kv_slot_addr, uint32_t accumulate,
+                                         uint32_t issue) {
   if (cell == kF16) {
+    const uint32_t v_addr = kv_slot_addr + 64 * D * 2;
     const uint32_t idesc = instr_desc(kFmtF16, kFmtF16, kAccF32, 128, D, 0, 1);
     constexpr uint32_t v_lbo = (D / 8) * 128;  // between 8-key groups
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-      mma_f16_ss(tmem_o, smem_desc(p_addr + k * 256, 128, 8 * 128),
-                 smem_desc(v_addr + k * 2 * v_lbo, v_lbo, 128), idesc, accumulate | (k > 0));
+      mma_f16_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 8 * 128),
+                 smem_desc(v_addr + k * 2 * v_lbo, v_lbo, 128), idesc, accumulate | (k > 0), issue);
   } else if (cell == kI8) {
+    const uint32_t v_addr = kv_slot_addr + 64 * D;
     const uint32_t idesc = instr_desc(kFmtE4M3, kFmtE4M3, kAccF32, 128, D, 0, 0);
 #pragma unroll
     for (int k = 0; k < 2; ++k)
-      mma_f8_ss(tmem_o, smem_desc(p_addr + k * 256, 128, 4 * 128),
-                smem_desc(v_addr + k * 256, 128, 4 * 128), idesc, accumulate | (k > 0));
+      mma_f8_ss(tmem + kColO, smem_desc(p_addr + k * 256, 128, 4 * 128),
+                smem_desc(v_addr + k * 256, 128, 4 * 128), idesc, accumulate | (k > 0), issue);
   } else {
-    const uint32_t vsf = v_addr + 32 * D;  // the scale block follows the codes in the unit
+    const uint32_t v_addr = kv_slot_addr + rec::kv_nvfp4_v_offset(D);
+    const uint32_t vsf = kv_slot_addr + rec::kv_nvfp4_vsf_offset(D);
     const uint32_t idesc = instr_desc_nvf4(128, D);
-    tmem_cp_32x128b_warpx4(tmem_sf + kSfbV, smem_desc(vsf, 128, 128));
-    mma_nvf4_ss(tmem_o, smem_desc(p_addr, 128, 2 * 128), smem_desc(v_addr, 128, 2 * 128), idesc,
-                accumulate, tmem_sfa_p, tmem_sf + kSfbV);
-  }
-}
-
-// position of stage g in a ring of `units` (units >= 3), advanced by the pipeline stride
-struct RingPos {
-  int slot;
-  uint32_t par;
-  __device__ __forceinline__ void advance(int by, int units) {
-    slot += by;
-    if (slot >= units) {
-      slot -= units;
-      par ^= 1u;
-    }
-  }
-};
-
-// Real keys and score scale of the pipeline's k-th stage (kept out of line: it runs once per
-// 32 stages and must not hold registers in the softmax loop).
-template <int D>
-__device__ __noinline__ void fetch_stage_meta(const AttnParams& p, const Plan& pl,
-                                              const int32_t* list, int head, int64_t q_index_i8,
-                                              int pi, int k, int& valid, float& scale) {
-  const int g = kPipes * k + pi;
-  valid = 0;
-  scale = 0.0f;
-  if (g >= pl.n) return;
-  const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
-  const int cell = cell_of(pl, g);
-  const int st = list ? list[g] : g;
-  valid = p.valid_k[st];
-  if (cell == kI8) {
-    scale = sigma * (p.o.q_int8_scale[q_index_i8] * p.o.k_int8_scale[(int64_t)head * p.stages + st]);
-  } else {
-    scale = cell == kNv ? sigma * p.s.q_global_scale * p.s.k_global_scale : sigma;
+    tmem_cp_32x128b_warpx4(tmem + kColSfbV, smem_desc(vsf, 128, 128), issue);
+    mma_nvf4_ss(tmem + kColO, smem_desc(p_addr, 128, 2 * 128), smem_desc(v_addr, 128, 2 * 128),
+                idesc, accumulate, tmem + kColSfaP, tmem + kColSfbV, issue);
   }
 }
 
@@ -442,7 +444,7 @@ __device__ __noinline__ void fetch_stage_meta(const AttnParams& p, const Plan& p
 // kernel
 // ------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int QB = p.s.query_block;
   const int head = blockIdx.y;
@@ -454,62 +456,49 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     if (ordered > 0) tile = ordered - 1;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef ATTN_PROFILE
-  const long long prof_start = clock64();
-#endif
 
   // ---- this tile's work list ----
-  Plan pl;
+  int cnt[3];
   const int32_t* list;
   if (p.dense_prefix) {
-    pl.c0 = 0;
-    pl.c01 = p.stages;
-    pl.n = p.stages;
+    cnt[0] = 0;
+    cnt[1] = p.stages;
+    cnt[2] = 0;
     list = nullptr;
   } else {
     const int32_t* rc = p.row_counts + ((int64_t)head * p.s.video_blocks + tile) * 4;
-    pl.c0 = rc[0];
-    pl.c01 = pl.c0 + rc[1];
-    pl.n = pl.c01 + rc[2];
+    cnt[0] = rc[0];
+    cnt[1] = rc[1];
+    cnt[2] = rc[2];
     list = p.stage_ids + (int64_t)head * p.capacity +
            p.row_offset[(int64_t)head * p.s.video_blocks + tile];
   }
-  if (pl.n == 0) return;
+  const int total = cnt[0] + cnt[1] + cnt[2];
+  if (total == 0) return;
   // After a give-up anywhere on this device the status word stays set: later CTAs (of this and
   // of later launches, until the host clears the word) return at once instead of each running
   // into its own wait limit.
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
-  const int n = pl.n;
 
   uint8_t* q_smem = smem;
-  uint8_t* p_smem = smem + p.p_off;
-  uint8_t* k_ring = smem + p.k_off;
-  uint8_t* v_ring = smem + p.v_off;
-  Scratch* sc = reinterpret_cast<Scratch*>(smem + p.misc_off);
-  Barriers* b = reinterpret_cast<Barriers*>(smem + p.misc_off + sizeof(Scratch));
+  uint8_t* p_smem = smem + p.q_region;
+  uint8_t* slots = p_smem + p.p_region;
+  float* colf = reinterpret_cast<float*>(slots + (size_t)p.ring_bytes);
+  Barriers* b = reinterpret_cast<Barriers*>(colf + D);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kMaxUnits; ++i) {
-      mbar_init(&b->k_full[i], 1);
-      mbar_init(&b->k_free[i], 1);
-      mbar_init(&b->v_full[i], 1);
-      mbar_init(&b->v_free[i], 1);
+    for (int i = 0; i < kMaxSlots; ++i) {
+      mbar_init(&b->kv_full[i], 1);
+      mbar_init(&b->kv_free[i], 1);
     }
     mbar_init(&b->q_full, 1);
-    for (int i = 0; i < kPipes; ++i) {
-      mbar_init(&b->s_full[i], 1);
-      mbar_init(&b->s_free[i], 4);
-      mbar_init(&b->p_full[i], 4);
-      mbar_init(&b->p_free[i], 1);
-      for (int w = 0; w < 4; ++w) {
-        mbar_init(&b->m_ready[i][w], 1);
-        mbar_init(&b->c_req[i][w], 1);
-        mbar_init(&b->c_ack[i][w], 1);
-      }
-    }
-    for (int i = 0; i < kPipes; ++i) mbar_init(&b->o_ok[i], 4);
-    for (int i = 0; i < 2; ++i) mbar_init(&b->pv_done[i], 1);
-    mbar_init(&b->all_done, kPipes);
+    mbar_init(&b->q_free, 1);
+    mbar_init(&b->s_full[0], 1);
+    mbar_init(&b->s_full[1], 1);
+    mbar_init(&b->s_free, kSoftmaxThreads / 32);
+    mbar_init(&b->p_full[0], kSoftmaxThreads / 32);
+    mbar_init(&b->p_full[1], kSoftmaxThreads / 32);
+    mbar_init(&b->all_done, 1);
     b->wc.abort = 0;
     b->wc.status = p.status;
     b->wc.limit_ns = p.wait_ns;
@@ -517,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   }
   // Query rows beyond QB (64-row tiles padded to the 128-row MMA shape) are never
   // initialised: rows are independent, their results stay in TMEM lanes nobody reads.
-  if (warp == kMmaWarp0) {
+  if (warp == kMmaWarp) {
     tmem_alloc(&b->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -525,398 +514,215 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = b->tmem_base;
-  WaitContext* const wc = &b->wc;
 
   const int q_index_fp = head * p.s.video_blocks + tile;  // q_fp16 / q_nvfp4 record
   const int64_t q_index_i8 =
       (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : tile);
   const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
-  const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
-  const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
 
-  // All four warps of a warpgroup execute the same setmaxnreg instruction, and each sits at the
-  // top of the branch whose code runs under the new register count.
+  // The second warpgroup (loader, MMA and two idle warps) hands most of its registers to the
+  // softmax warpgroup.  All four warps of a warpgroup execute the same setmaxnreg instruction,
+  // and each sits at the top of the branch whose code runs under the new register count.
   if (warp >= kLoaderWarp) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
-    if (warp == kLoaderWarp) {
-      // =============================== loader ===============================
-      // The whole warp runs the loop with uniform control flow (list entries are fetched 32 at
-      // a time, one per lane); one lane issues the copies.  The key parts and the value parts
-      // of the stage records go to two rings with cursors of their own: a key unit is free as
-      // soon as its QK has run, a value unit only after its PV.
-      const uint32_t lead = lane == 0;
-      {
-        uint32_t total = 0;
-        if (pl.c0 > 0) total += (uint32_t)rec::q_nvfp4_bytes(QB, D);
-        if (pl.c01 > pl.c0) total += (uint32_t)rec::q_int8_bytes(QB, D);
-        if (pl.n > pl.c01) total += (uint32_t)rec::q_fp16_bytes(QB, D);
-        mbar_arrive_expect_tx(&b->q_full, total, lead);
-        if (pl.c0 > 0) {
-          const int qbytes = (int)rec::q_nvfp4_bytes(QB, D);
-          const uint8_t* src = static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes;
-          uint8_t* dst = q_smem + p.q_off[kNv];
-          if (QB == 64) {
-            // codes fill the first half of the 128-row tile; scale blocks follow the full tile
-            const int codes = QB * D / 2;
-            bulk_g2s(dst, src, codes, &b->q_full, lead);
-            bulk_g2s(dst + 128 * D / 2, src + codes, qbytes - codes, &b->q_full, lead);
-          } else {
-            bulk_g2s(dst, src, qbytes, &b->q_full, lead);
-          }
-        }
-        if (pl.c01 > pl.c0) {
-          const int qbytes = (int)rec::q_int8_bytes(QB, D);
-          bulk_g2s(q_smem + p.q_off[kI8],
-                   static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes, qbytes, &b->q_full,
-                   lead);
-        }
-        if (pl.n > pl.c01) {
-          const int qbytes = (int)rec::q_fp16_bytes(QB, D);
-          bulk_g2s(q_smem + p.q_off[kF16],
-                   static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes, qbytes,
-                   &b->q_full, lead);
-        }
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+  if (warp == kLoaderWarp) {
+    // =============================== loader ===============================
+    // The whole warp walks the list with uniform control flow; one lane issues.
+    const uint32_t lead = lane == 0;
+    int phase_ord = 0;
+    uint32_t filled = 0, fillpar = 0;  // per slot: ever filled / parity of the fill count
+    for (int cell = 0; cell < 3; ++cell) {
+      if (cnt[cell] == 0) continue;
+      if (phase_ord > 0) wait<kPark>(&b->wc, &b->q_free, (phase_ord - 1) & 1, 1);
+      const int qbytes = CellInfo<D>::q_bytes(cell, QB);
+      const uint8_t* qsrc =
+          cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
+          : cell == kI8 ? static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes
+                        : static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes;
+      mbar_arrive_expect_tx(&b->q_full, qbytes, lead);
+      if (cell == kNv && QB == 64) {
+        // codes fill the first half of the 128-row tile; scale blocks follow the full tile
+        const int codes = QB * D / 2;
+        bulk_g2s(q_smem, qsrc, codes, &b->q_full, lead);
+        bulk_g2s(q_smem + 128 * D / 2, qsrc + codes, qbytes - codes, &b->q_full, lead);
+      } else {
+        bulk_g2s(q_smem, qsrc, qbytes, &b->q_full, lead);
       }
-      int win0 = -64, stage_l = 0;  // window of 32 list entries held one per lane
-      int cur[2] = {0, 0};          // next stage whose key (0) / value (1) part is to be loaded
-      int slot[2] = {0, 0};
-      uint32_t fills[2] = {0, 0};   // per unit: parity of the number of fills so far
-      uint64_t t0 = 0;
-      int idle = 0;
-      while (cur[0] < n || cur[1] < n) {
-        bool progress = false;
+      const int kvbytes = CellInfo<D>::kv_bytes(cell);
+      const uint8_t* kvbase =
+          (cell == kNv ? static_cast<const uint8_t*>(p.o.kv_nvfp4)
+           : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
+                         : static_cast<const uint8_t*>(p.o.kv_fp16)) +
+          (int64_t)head * p.stages * kvbytes;
+      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      // The ring is cut into equal slots of this phase's record size; slots of the
+      // previous phase must all be released before the new geometry is written.
+      const int slot_bytes = (kvbytes + 127) & ~127;
+      const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
+      for (int sl = 0; sl < kMaxSlots; ++sl)
+        if ((filled >> sl) & 1u)
+          wait<kPark>(&b->wc, &b->kv_free[sl], ((fillpar >> sl) & 1u) ^ 1u, 2);
+      int stage_l = 0;  // list entries, 32 at a time, one per lane
+      int slot = -1;
+      for (int i = 0; i < cnt[cell]; ++i) {
+        if ((i & 31) == 0 && list != nullptr && i + lane < cnt[cell])
+          stage_l = list[first + i + lane];
+        const int stage = list ? __shfl_sync(0xffffffffu, stage_l, i & 31) : i;
+        slot = slot + 1 == nslot ? 0 : slot + 1;
+        if ((filled >> slot) & 1u)
+          wait<kPark>(&b->wc, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, 2);
+        mbar_arrive_expect_tx(&b->kv_full[slot], kvbytes, lead);
+        bulk_g2s(slots + (size_t)slot * slot_bytes, kvbase + (int64_t)stage * kvbytes, kvbytes,
+                 &b->kv_full[slot], lead);
+        filled |= 1u << slot;
+        fillpar ^= 1u << slot;
+      }
+      ++phase_ord;
+    }
+  } else if (warp == kMmaWarp) {
+    // =============================== MMA issue ===============================
+    // Uniform control flow for the whole warp (descriptors stay warp-uniform values);
+    // only the tcgen05 instructions themselves are predicated on one lane.
+    const uint32_t lead = lane == 0;
+    int g = 0, phase_ord = 0;
+    uint32_t usepar = 0;  // per slot: parity of the number of fills consumed
+    const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+    for (int cell = 0; cell < 3; ++cell) {
+      if (cnt[cell] == 0) continue;
+      wait<kPark>(&b->wc, &b->q_full, phase_ord & 1, 3);
+      tc_fence_after_sync();
+      if (cell == kNv) {
+        const uint32_t qsf = q_addr + 128 * D / 2;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          const int g = cur[part];
-          if (g >= n) continue;
-          const int units = part ? p.v_units : p.k_units;
-          uint64_t* full = part ? b->v_full : b->k_full;
-          uint64_t* free_bar = part ? b->v_free : b->k_free;
-          const int u = slot[part];
-          // fill f of a unit may start once the MMA that read fill f-1 is complete
-          int ok = g < units || mbar_test_wait(&free_bar[u], ((fills[part] >> u) & 1u) ^ 1u);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) continue;
-          if (list != nullptr && (g < win0 || g >= win0 + 32)) {
-            win0 = g;
-            stage_l = win0 + lane < n ? list[win0 + lane] : 0;
-          }
-          const int cell = cell_of(pl, g);
-          const int stage = list ? __shfl_sync(0xffffffffu, stage_l, (g - win0) & 31) : g;
-          const int rb = rec_bytes<D>(cell);
-          const uint8_t* src =
-              (cell == kNv ? static_cast<const uint8_t*>(p.o.kv_nvfp4)
-               : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
-                             : static_cast<const uint8_t*>(p.o.kv_fp16)) +
-              ((int64_t)head * p.stages + stage) * rb;
-          uint8_t* dst = part ? v_ring + u * p.v_unit : k_ring + u * p.k_unit;
-          const int bytes = part ? v_bytes<D>(cell) : k_bytes<D>(cell);
-          mbar_arrive_expect_tx(&full[u], (uint32_t)bytes, lead);
-          if (cell == kNv) {
-            // codes, then the scale blocks behind them
-            const int sf = part ? 512 : (D / 64) * 512;
-            bulk_g2s(dst, src + (part ? rec::kv_nvfp4_v_offset(D) : 0), 32 * D, &full[u], lead);
-            bulk_g2s(dst + 32 * D,
-                     src + (part ? rec::kv_nvfp4_vsf_offset(D) : rec::kv_nvfp4_ksf_offset(D)), sf,
-                     &full[u], lead);
-          } else {
-            bulk_g2s(dst, src + (part ? (rb >> 1) : 0), bytes, &full[u], lead);
-          }
-          fills[part] ^= 1u << u;
-          slot[part] = u + 1 == units ? 0 : u + 1;
-          cur[part] = g + 1;
-          progress = true;
-        }
-        if (progress) {
-          idle = 0;
-          t0 = 0;
-        } else {
-          asm volatile("nanosleep.u32 100;");
-          if (++idle >= 32) {
-            idle = 0;
-            if (b->wc.abort) break;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > p.wait_ns) {
-              b->wc.abort = 1;
-              atomicCAS(p.status, 0, 1);
-              break;
-            }
-          }
-        }
+        for (int k = 0; k < D / 64; ++k)
+          tmem_cp_32x128b_warpx4(tmem + kColSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128),
+                                 lead);
       }
-      // Unwinding after a give-up: copies already issued must land before the CTA returns
-      // its shared memory (on the normal path the MMA warps have consumed every one of them).
-      if (b->wc.abort) {
-        for (int u = 0; u < kMaxUnits; ++u) {
-          if (u < p.k_units && u < cur[0]) drain_wait(&b->k_full[u], ((fills[0] >> u) & 1u) ^ 1u, 1000000ull);
-          if (u < p.v_units && u < cur[1]) drain_wait(&b->v_full[u], ((fills[1] >> u) & 1u) ^ 1u, 1000000ull);
-        }
-        drain_wait(&b->q_full, 0, 1000000ull);
-      }
-    } else {
-      // =============================== MMA issue (one warp per pipeline) =====================
-      const int pi = warp - kMmaWarp0;
-      if (lane == 0) {
-        const uint32_t q_base = smem_u32(q_smem);
-        const uint32_t p_addr = smem_u32(p_smem) + pi * kPBytes;
-        const uint32_t k_base = smem_u32(k_ring), v_base = smem_u32(v_ring);
-        const uint32_t tmem_s = tmem + kColS + 64 * pi;
-        const uint32_t tmem_sf = tmem + kColSf + 20 * pi;
-        wait<100>(wc, &b->q_full, 0, 3);
-        tc_fence_after_sync();
-        if (pl.c0 > 0) {
-          const uint32_t qsf = q_base + p.q_off[kNv] + 128 * D / 2;
-#pragma unroll
-          for (int k = 0; k < D / 64; ++k)
-            tmem_cp_32x128b_warpx4(tmem_sf + kSfaQ + 4 * k, smem_desc(qsf + 512 * k, 128, 128));
-        }
-        // QK of the pipeline's next stage is issued as soon as the softmax warps have read the
-        // scores of the current one, PV of the current one when its P is written and its
-        // accumulator corrected: in this order, which is the order the events happen in.
-        RingPos kq{pi % p.k_units, 0}, vq{pi % p.v_units, 0};
-        if (pi < n) {
-          wait<50>(wc, &b->k_full[kq.slot], kq.par, 4);
+      const int n = cnt[cell];
+      const int slot_bytes = (CellInfo<D>::kv_bytes(cell) + 127) & ~127;
+      const int nslot = min(kMaxSlots, p.ring_bytes / slot_bytes);
+      const uint32_t ring_addr = smem_u32(slots);
+      // software pipeline: QK of stage i+1 is issued before PV of stage i
+      int qk_slot = 0, pv_slot = 0;
+      for (int i = 0; i <= n; ++i) {
+        if (i < n) {
+          const int gi = g + i;
+          const int slot = qk_slot;
+          qk_slot = qk_slot + 1 == nslot ? 0 : qk_slot + 1;
+          wait<kPark>(&b->wc, &b->kv_full[slot], (usepar >> slot) & 1u, 4);
+          usepar ^= 1u << slot;
+          const int sb = s_buffer(cell, gi);
+          // single score buffer of the NVFP4 phase (always the first phase: gi == i)
+          if (cell == kNv && i > 0) wait<kPark>(&b->wc, &b->s_free, (uint32_t)(i - 1) & 1u, 5);
           tc_fence_after_sync();
-          const int cell = cell_of(pl, pi);
-          issue_qk<D>(cell, tmem_s, tmem_sf, q_base + p.q_off[cell], k_base + kq.slot * p.k_unit);
-          mma_commit(&b->s_full[pi]);
-          mma_commit(&b->k_free[kq.slot]);
+          const uint32_t slot_addr = ring_addr + slot * slot_bytes;
+          issue_qk<D>(cell, tmem + s_column(sb), tmem, q_addr, slot_addr, slot_addr, lead);
+          mma_commit(&b->s_full[sb], lead);
+          if (i == n - 1) mma_commit(&b->q_free, lead);
         }
-        int k = 0;
-        for (int g = pi; g < n; g += kPipes, ++k) {
-          const int gn = g + kPipes;
-          if (gn < n) {
-            kq.advance(kPipes, p.k_units);
-            wait<50>(wc, &b->k_full[kq.slot], kq.par, 4);
-            wait<20>(wc, &b->s_free[pi], k & 1, 5);
-            tc_fence_after_sync();
-            const int cell = cell_of(pl, gn);
-            issue_qk<D>(cell, tmem_s, tmem_sf, q_base + p.q_off[cell], k_base + kq.slot * p.k_unit);
-            mma_commit(&b->s_full[pi]);
-            mma_commit(&b->k_free[kq.slot]);
-          }
-          const int acc = g & 1;
-          wait<50>(wc, &b->v_full[vq.slot], vq.par, 6);
-          wait<20>(wc, &b->p_full[pi], k & 1, 7);
-          wait<20>(wc, &b->o_ok[pi], k & 1, 8);
+        if (i > 0) {
+          const int gj = g + i - 1;
+          const int slot = pv_slot;
+          pv_slot = pv_slot + 1 == nslot ? 0 : pv_slot + 1;
+          wait<kPark>(&b->wc, &b->p_full[gj & 1], (gj >> 1) & 1, 6);
           tc_fence_after_sync();
-          issue_pv<D>(cell_of(pl, g), tmem + kColO + 128 * acc, tmem_sf, tmem + kColSfaP, p_addr,
-                      v_base + vq.slot * p.v_unit, g >= 2);
-          mma_commit(&b->pv_done[acc]);
-          mma_commit(&b->p_free[pi]);
-          mma_commit(&b->v_free[vq.slot]);
-          vq.advance(kPipes, p.v_units);
-        }
-        // The end of the tile is signalled on a barrier of its own (one arrival per MMA warp);
-        // each MMA lane also waits for it, so that no MMA is in flight when tensor memory is
-        // given back.
-        mma_commit(&b->all_done);
-        if (!drain_wait(&b->all_done, 0, p.wait_ns)) {
-          b->wc.abort = 1;
-          atomicCAS(p.status, 0, 9);
+          const uint32_t slot_addr = ring_addr + slot * slot_bytes;
+          issue_pv<D>(cell, tmem, p_addr + p_buffer(cell, gj) * p_tile_bytes(cell), slot_addr,
+                      gj > 0, lead);
+          mma_commit(&b->kv_free[slot], lead);  // also tells the softmax warps this PV is done
         }
       }
-      __syncwarp();
+      g += n;
+      ++phase_ord;
     }
-  } else if (warp >= kCorrectionWarp0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCorrectionRegs));
-    // =============================== correction ===============================
-    const int cw = warp - kCorrectionWarp0;
-    const int row = cw * 32 + lane;
-    const uint32_t lane_base = (uint32_t)(cw * 32) << 16;
-    // per-channel factors that move O from one phase's value domain into the next one's
-    for (int c = threadIdx.x - kCorrectionWarp0 * 32; c < D; c += 128) {
-      const float i8 = vscale != nullptr ? vscale[c] * kFp8OffsetInv : 0.0f;
-      sc->dom_i8[c] = i8;
-      sc->colf[0][c] = i8 == 0.0f ? 0.0f : nv_dom / i8;
-      sc->colf[1][c] = nv_dom;
-      sc->colf[2][c] = i8;
-    }
-    asm volatile("bar.sync 2, 128;" ::: "memory");
-    int pi = 0, k = 0;  // stage g = 3 k + pi
-    for (int g = 0; g < n; ++g) {
-      const int acc = g & 1;
-      wait<20>(wc, &b->c_req[pi][cw], k & 1, 30);
-      const int flag = sc->flag[pi][cw];
-      const float alpha = (flag & 1) ? sc->alpha[pi][row] : 1.0f;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&b->c_ack[pi][cw]);
-      // The previous PV into this accumulator must be complete before it is touched.  The wait
-      // is made even when nothing is rescaled: a barrier's phase may only complete after its
-      // waiter has seen the phase before it, and o_ok of stage g+3 (same pipeline, same MMA
-      // warp) is then signalled after stage g+2 waited here for PV of stage g, which that MMA
-      // warp issued after it saw o_ok of stage g.
-      if (g >= 2) wait<20>(wc, &b->pv_done[acc], ((g >> 1) - 1) & 1, 31);
-      if (flag & 1) {
-        tc_fence_after_sync();
-        const int from = (flag >> 4) & 3, to = (flag >> 8) & 3;
-        const float* colf =
-            from == to ? nullptr : sc->colf[from == kNv ? (to == kI8 ? 0 : 1) : 2];
-        rescale_o<D>(tmem + lane_base + kColO + 128 * acc, alpha, colf);
-        tc_fence_before_sync();
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&b->o_ok[pi]);
-      if (++pi == kPipes) {
-        pi = 0;
-        ++k;
-      }
-    }
+    // The end of the tile is signalled on a barrier of its own.
+    mma_commit(&b->all_done, lead);
+  }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     // =============================== softmax rows ===============================
-    const int pi = warp >> 2;                    // pipeline
-    const int w = warp & 3;                      // warp of the pipeline = TMEM lane quarter
-    const int row = w * 32 + lane;               // query row == TMEM lane
-    const uint32_t lane_base = (uint32_t)(w * 32) << 16;
-    const uint32_t tmem_s = tmem + lane_base + kColS + 64 * pi;
-    const bool live_warp = w * 32 < QB;
-    const bool lead = lane == 0;
-    const int prev_pi = pi == 0 ? kPipes - 1 : pi - 1;   // pipeline of stage g-1
-    const int prev2_pi = pi == kPipes - 1 ? 0 : pi + 1;  // pipeline of stage g-2
-    uint8_t* p_tile = p_smem + pi * kPBytes;
-    if (pl.c0 > 0) {
-      tmem_st4(tmem + lane_base + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
+    const int row = warp * 32 + lane;            // query row == TMEM lane
+    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
+    RowState st{-5.0e6f, 0.0f};
+    int s_use0 = 0, s_use1 = 0;  // stages consumed from each score buffer so far
+    uint32_t pvpar = 0;         // per slot: parity of the number of PVs that used it
+    int prev_slot = 0;
+    uint32_t prev_slot_parity = 0;
+    int g = 0;
+    int prev_cell = -1;
+    const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
+    const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
+    const bool live_warp = warp * 32 < QB;
+    if (cnt[kNv] > 0) {
+      tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
       tmem_wait_st();
     }
-    float m_own = -5.0e6f, d = 0.0f;
-    // Metadata of 32 of the pipeline's stages (real keys and score scale), one stage per lane,
-    // fetched one batch ahead of its use.
-    int nx_valid = 0, cu_valid = 0;
-    float nx_scale = 0.0f, cu_scale = 0.0f;
-    auto fetch_meta = [&](int k0) { fetch_stage_meta<D>(p, pl, list, head, q_index_i8, pi, k0 + lane, nx_valid, nx_scale); };
-    fetch_meta(0);
-    int k = 0;
-    for (int g = pi; g < n; g += kPipes, ++k) {
-      if ((k & 31) == 0) {
-        cu_valid = nx_valid;
-        cu_scale = nx_scale;
-        fetch_meta(k + 32);
-      }
-      const int cell = cell_of(pl, g);
-      const int valid = __shfl_sync(0xffffffffu, cu_valid, k & 31);
-      const float scale = __shfl_sync(0xffffffffu, cu_scale, k & 31);
-      {
-        PROF_BEGIN();
-        wait(wc, &b->s_full[pi], k & 1, 10 + cell);
-        PROF_END(0 + cell);
-      }
-      PROF_BEGIN();
-      tc_fence_after_sync();
-      if (!live_warp) {
-        // padding rows of a 64-row tile: keep the barrier protocol, skip the math
-        if (k > 0) wait(wc, &b->c_ack[pi][w], (k - 1) & 1, 14);
-        if (lead) {
-          mbar_arrive(&b->s_free[pi]);
-          sc->flag[pi][w] = 0;
-          mbar_arrive(&b->c_req[pi][w]);
+    for (int cell = 0; cell < 3; ++cell) {
+      if (cnt[cell] == 0) continue;
+      if (prev_cell >= 0) {
+        // per-channel factor that moves O from the previous phase's domain into this one's
+        asm volatile("bar.sync 5, 128;" ::: "memory");
+        for (int c = threadIdx.x; c < D; c += kSoftmaxThreads) {
+          const float from = prev_cell == kNv ? nv_dom
+                                              : (prev_cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f);
+          const float to = cell == kI8 ? vscale[c] * 0.0022326917f : 1.0f;
+          colf[c] = to == 0.0f ? 0.0f : from / to;
         }
-        if (k > 0) wait(wc, &b->p_free[pi], (k - 1) & 1, 15);
-        if (lead) mbar_arrive(&b->p_full[pi]);
-        continue;
+        asm volatile("bar.sync 5, 128;" ::: "memory");
       }
-      uint32_t r[64];
-      tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(r));
-      tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
-      tmem_wait_ld();
-      // the scores are in registers: the MMA warp may overwrite the buffer (QK of stage g+3)
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lead) mbar_arrive(&b->s_free[pi]);
-
-      const float m_loc = stage_max(r, cell == kI8, valid) * scale;
-
-      // one running maximum for all pipelines: take the latest (stage g-1), publish ours
-      float m_prev = -5.0e6f, m_prev2 = -5.0e6f;
-      if (g > 0) {
-        PROF_END(9);
-        {
-          PROF_BEGIN();
-          wait(wc, &b->m_ready[prev_pi][w], (pi == 0 ? k - 1 : k) & 1, 16);
-          PROF_END(4);
+      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      const float q_scale =
+          cell == kI8 ? p.o.q_int8_scale[q_index_i8] : 1.0f;
+      const float base_scale =
+          cell == kNv ? sigma * p.s.q_global_scale * p.s.k_global_scale : sigma;
+      // Per-stage metadata (stage id -> real keys, key scale) is fetched 32 stages at a
+      // time, one stage per lane, and handed out with shuffles: no dependent global
+      // loads sit on the per-stage critical path.
+      int meta_valid = 64;
+      float meta_scale = 1.0f;
+      const int nslot = min(kMaxSlots, p.ring_bytes / ((CellInfo<D>::kv_bytes(cell) + 127) & ~127));
+      const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
+      int slot = 0;
+      for (int i = 0; i < cnt[cell]; ++i, ++g) {
+        if ((i & 31) == 0) {
+          const int mine = i + lane;
+          if (mine < cnt[cell]) {
+            const int stage = list ? list[first + mine] : mine;
+            meta_valid = p.valid_k[stage];
+            if (cell == kI8) meta_scale = sigma * (q_scale * kscale[stage]);
+          }
         }
-        m_prev = sc->m[prev_pi][row];
-        if (g > 1) m_prev2 = sc->m[prev2_pi][row];  // after stage g-2: what the accumulator refers to
+        const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
+        const bool phase_first = i == 0 && prev_cell >= 0;
+        const int sb = s_buffer(cell, g);
+        const uint32_t s_parity = (sb ? s_use1 : s_use0) & 1;
+        s_use0 += sb ? 0 : 1;
+        s_use1 += sb ? 1 : 0;
+        // barrier that the PV of the previous stage completes (its key/value slot release)
+        uint64_t* pv_bar = &b->kv_free[prev_slot];
+        const uint32_t pv_parity = prev_slot_parity;
+        prev_slot = slot;
+        prev_slot_parity = (pvpar >> slot) & 1u;
+        pvpar ^= 1u << slot;
+        slot = slot + 1 == nslot ? 0 : slot + 1;
+        const float sc =
+            cell == kI8 ? __shfl_sync(0xffffffffu, meta_scale, i & 31) : base_scale;
+        softmax_stage<D>(b, p, p_smem, colf, tmem_row, row, cell, g, phase_first, sc, valid,
+                         live_warp, sb, s_parity, pv_bar, pv_parity, st);
       }
-      const float m_new = fmaxf(m_prev, m_loc);
-      sc->m[pi][row] = m_new;
-      __syncwarp();
-      if (lead) mbar_arrive(&b->m_ready[pi][w]);
-
-      // the accumulator of this stage was last touched by stage g-2
-      const float alpha_acc = ex2(m_prev2 - m_new);
-      const int cell2 = g > 1 ? cell_of(pl, g - 2) : cell;
-      const bool need = g > 1 && (cell != cell2 || __any_sync(0xffffffffu, alpha_acc != 1.0f));
-      if (k > 0) {
-        PROF_BEGIN();
-        wait(wc, &b->c_ack[pi][w], (k - 1) & 1, 17);  // previous request has been read
-        PROF_END(5);
-      }
-      if (need) sc->alpha[pi][row] = alpha_acc;
-      if (lead) sc->flag[pi][w] = need ? (1 | (cell2 << 4) | (cell << 8)) : 0;
-      __syncwarp();
-      if (lead) mbar_arrive(&b->c_req[pi][w]);
-
-      // exponent = s * scale + bias; the NVFP4 cell produces 6 P directly (e2m1 input range),
-      // the INT8 cell P * 2^8.807 (e4m3 input range); the sums are scaled back.
-      const float bias = cell == kI8 ? kFp8Offset - m_new
-                                     : (cell == kNv ? 2.5849625007f - m_new : -m_new);
-      const float sum_scale = cell == kI8 ? kFp8OffsetInv : (cell == kNv ? 0.16666667f : 1.0f);
-      const float sum = stage_exp(r, scale, bias);
-      d = d * ex2(m_own - m_new) + sum * sum_scale;  // this pipeline's share of the denominator
-      m_own = m_new;
-
-      // the P tile is free once the pipeline's previous PV has read it
-      if (k > 0) {
-        PROF_BEGIN();
-        wait(wc, &b->p_free[pi], (k - 1) & 1, 20 + cell);
-        PROF_END(6);
-      }
-      if (cell == kNv) {
-        write_p<kNv>(p_tile, row, r);
-      } else if (cell == kI8) {
-        write_p<kI8>(p_tile, row, r);
-      } else {
-        write_p<kF16>(p_tile, row, r);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lead) mbar_arrive(&b->p_full[pi]);
-      PROF_END(7);
-#ifdef ATTN_PROFILE
-      if (lead) atomicAdd(&g_prof[8], 1ull);
-#endif
+      prev_cell = cell;
     }
-    // ---- epilogue: merge the accumulators, O_true / d -> fp16, packed row order ----
-    sc->fin_m[pi][row] = m_own;
-    sc->fin_d[pi][row] = d;
-    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
-    wait(wc, &b->all_done, 0, 40);
+    // ---- epilogue: O_true / d -> fp16, packed row order ----
+    wait(&b->wc, &b->all_done, 0, 7);
     if (live_warp) {
       tc_fence_after_sync();
-      const int last_pi = (n - 1) % kPipes;
-      const float mf = sc->m[last_pi][row];  // maximum after the last stage
-      float dsum = 0.0f;
-#pragma unroll
-      for (int q = 0; q < kPipes; ++q)
-        if (q < n) dsum += sc->fin_d[q][row] * ex2(sc->fin_m[q][row] - mf);
-      const float inv = 1.0f / dsum;
-      // accumulator of the last stage refers to mf; the other one to the maximum after stage n-2
-      const int acc1 = (n - 1) & 1;
-      const bool has2 = n > 1;
-      const int cell1 = cell_of(pl, n - 1), cell2 = has2 ? cell_of(pl, n - 2) : 0;
-      const float g1 = inv;
-      const float g2 = has2 ? ex2(sc->m[last_pi == 0 ? kPipes - 1 : last_pi - 1][row] - mf) * inv : 0.0f;
+      const float inv = 1.0f / st.d;
       const bool live = row < QB;
       __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)tile * QB + row) * D;
-      // the pipelines' warpgroups share the channels in chunks of 32
 #pragma unroll 1
-      for (int c0 = 32 * pi; c0 < D; c0 += 32 * kPipes) {
-        uint32_t a[32], bb[32];
-        tmem_ld32(tmem + lane_base + kColO + 128 * acc1 + c0, a);
-        if (has2) tmem_ld32(tmem + lane_base + kColO + 128 * (acc1 ^ 1) + c0, bb);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_row + kColO + c0, r);
         tmem_wait_ld();
         if (live) {
 #pragma unroll
@@ -925,19 +731,15 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
             __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              float o[2];
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int c = c0 + j + 2 * i + e;
-                const float d1 = cell1 == kNv ? nv_dom : (cell1 == kI8 ? sc->dom_i8[c] : 1.0f);
-                float accv = __uint_as_float(a[j + 2 * i + e]) * d1 * g1;
-                if (has2) {
-                  const float d2 = cell2 == kNv ? nv_dom : (cell2 == kI8 ? sc->dom_i8[c] : 1.0f);
-                  accv += __uint_as_float(bb[j + 2 * i + e]) * d2 * g2;
-                }
-                o[e] = accv;
+              float a = __uint_as_float(r[j + 2 * i]), c = __uint_as_float(r[j + 2 * i + 1]);
+              if (prev_cell == kNv) {
+                a *= nv_dom;
+                c *= nv_dom;
+              } else if (prev_cell == kI8) {
+                a *= vscale[c0 + j + 2 * i] * 0.0022326917f;
+                c *= vscale[c0 + j + 2 * i + 1] * 0.0022326917f;
               }
-              h[i] = __floats2half2_rn(o[0], o[1]);
+              h[i] = __floats2half2_rn(a * inv, c * inv);
             }
             *reinterpret_cast<uint4*>(dst + c0 + j) = v;
           }
@@ -948,59 +750,41 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp0) tmem_dealloc(tmem, kTmemCols);
-#ifdef ATTN_PROFILE
-  if (threadIdx.x == 0) {
-    atomicAdd(&g_prof[21], (unsigned long long)(clock64() - prof_start));
-    atomicAdd(&g_prof[22], 1ull);
-    atomicAdd(&g_prof[23], (unsigned long long)n);
-  }
-#endif
+  if (warp == kMmaWarp) tmem_dealloc(tmem, kTmemCols);
 }
 
 template <int D>
 int launch(AttnParams& p, int tiles, cudaStream_t st) {
+  const int QB = p.s.query_block;
+  int q_region = 0, p_region = 0, slot = 0;
   const bool nv = p.s.has_nvfp4 && !p.dense_prefix, f16 = p.s.has_fp16 && !p.dense_prefix;
-  int off = 0, ku = 0, vu = 0;
-  p.q_off[kNv] = p.q_off[kI8] = p.q_off[kF16] = 0;
   if (nv) {
-    p.q_off[kNv] = off;
-    off += (128 * D / 2 + (D / 64) * 512 + 1023) & ~1023;
-    ku = max(ku, k_bytes<D>(kNv));
-    vu = max(vu, v_bytes<D>(kNv));
+    q_region = max(q_region, 128 * D / 2 + (D / 64) * 512);
+    p_region = max(p_region, 2 * 128 * 32);
+    slot = max(slot, (int)rec::kv_nvfp4_bytes(D));
   }
   if (p.s.has_int8) {
-    p.q_off[kI8] = off;
-    off += 128 * D;
-    ku = max(ku, k_bytes<D>(kI8));
-    vu = max(vu, v_bytes<D>(kI8));
+    q_region = max(q_region, 128 * D);
+    p_region = max(p_region, 2 * 128 * 64);
+    slot = max(slot, (int)rec::kv_int8_bytes(D));
   }
   if (f16) {
-    p.q_off[kF16] = off;
-    off += 128 * D * 2;
-    ku = max(ku, k_bytes<D>(kF16));
-    vu = max(vu, v_bytes<D>(kF16));
+    q_region = max(q_region, 128 * D * 2);
+    p_region = max(p_region, 128 * 128);
+    slot = max(slot, (int)rec::kv_fp16_bytes(D));
   }
-  ku = (ku + 127) & ~127;
-  vu = (vu + 127) & ~127;
-  p.p_off = off;
-  off += kPipes * kPBytes;
-  const int misc = (int)((sizeof(Scratch) + sizeof(Barriers) + 127) & ~127);
-  const int ring = kSmemLimit - off - misc;
-  // Every barrier is waited on phase by phase by one waiter: a pipeline's MMA warp must meet
-  // the same units again and again, so both rings hold a multiple of kPipes units (stage g
-  // uses unit g % units, pipeline g % kPipes).  Key units turn over quickly (free after QK),
-  // value units are held until PV.
-  p.k_unit = ku;
-  p.v_unit = vu;
-  p.k_units = p.v_units = kPipes;
-  if (ring < kPipes * (ku + vu)) return ANEMOI_SM100_ELAUNCH;
-  if (ring >= kPipes * (ku + 2 * vu)) p.v_units = 2 * kPipes;
-  if (ring >= 2 * kPipes * (ku + vu)) p.k_units = 2 * kPipes;
-  p.k_off = off;
-  p.v_off = off + p.k_units * ku;
-  p.misc_off = p.v_off + p.v_units * vu;
-  const size_t smem = (size_t)p.misc_off + misc;
+  (void)QB;
+  q_region = (q_region + 1023) & ~1023;
+  const int fixed = q_region + p_region + D * 4 + (int)sizeof(Barriers);
+  // two CTAs per SM: measured limit is 115,528 bytes of dynamic shared memory per CTA
+  const int budget = 115528;
+  int ring = ((budget - fixed) / 128) * 128;
+  ring = max(ring, 2 * ((slot + 127) & ~127));
+  ring = min(ring, kMaxSlots * ((slot + 127) & ~127));
+  p.ring_bytes = ring;
+  p.q_region = q_region;
+  p.p_region = p_region;
+  const size_t smem = (size_t)fixed + (size_t)ring;
   auto kernel = attention_kernel<D>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
@@ -1033,24 +817,13 @@ __global__ void wait_selftest_kernel(uint64_t limit_ns, int32_t* status) {
     mbar_init_fence();
   }
   __syncthreads();
-  if (threadIdx.x == 0) wait<50>(&wc, &bar, 0, 99);
+  if (threadIdx.x == 0) wait(&wc, &bar, 0, 99);
   __syncthreads();
   // every other thread's wait must now return at once
   if (threadIdx.x != 0) wait(&wc, &bar, 0, 98);
 }
 
 }  // namespace
-
-#ifdef ATTN_PROFILE
-extern "C" int anemoi_sm100_debug_profile(unsigned long long* host64, int reset) {
-  if (cudaMemcpyFromSymbol(host64, g_prof, sizeof(g_prof)) != cudaSuccess) return -2;
-  if (reset) {
-    static unsigned long long zeros[64];
-    if (cudaMemcpyToSymbol(g_prof, zeros, sizeof(zeros)) != cudaSuccess) return -2;
-  }
-  return 0;
-}
-#endif
 
 extern "C" int anemoi_sm100_set_wait_limit_ns(uint64_t limit_ns) {
   if (limit_ns == 0) return ANEMOI_SM100_EINVAL;

@@ -27,16 +27,24 @@ struct WaitContext {
   uint64_t limit_ns;
 };
 
-// kSleepNs > 0: sleep between polls (roles that mostly wait and must not take issue slots
-// from the arithmetic warps of their scheduler).
-template <int kSleepNs>
+// Two flavours.  kSpin: tight polls (the softmax rows, whose hand-offs are on the critical path
+// and arrive within tens of cycles).  kPark: mbarrier.try_wait with a suspend-time hint parks the
+// thread in hardware until the phase completes or the hint runs out, so a role that mostly waits
+// (loader, MMA issue) takes no issue slots from the arithmetic warps of its scheduler.  Between
+// batches of polls, or parked tries, the waiter looks at the abort flag and the clock.
+enum WaitMode : int { kSpin = 0, kPark = 1 };
+constexpr uint32_t kParkNs = 2000;
+
+template <int kMode>
 __device__ __noinline__ void wait_slow(WaitContext* w, uint64_t* bar, uint32_t parity, int where) {
   uint64_t t0 = 0;
   for (;;) {
+    if (kMode == kPark) {
+      if (mbar_try_wait_hint(bar, parity, kParkNs)) return;
+    } else {
 #pragma unroll 1
-    for (int k = 0; k < (kSleepNs > 0 ? 32 : 128); ++k) {
-      if (mbar_try_wait(bar, parity)) return;
-      if (kSleepNs > 0) asm volatile("nanosleep.u32 %0;" ::"n"(kSleepNs));
+      for (int k = 0; k < 256; ++k)
+        if (mbar_try_wait(bar, parity)) return;
     }
     if (w->abort) return;
     const uint64_t now = globaltimer_ns();
@@ -47,10 +55,11 @@ __device__ __noinline__ void wait_slow(WaitContext* w, uint64_t* bar, uint32_t p
   atomicCAS(w->status, 0, where);
 }
 
-template <int kSleepNs = 0>
+// One inline poll; the bounded loop is a shared out-of-line function (code size).
+template <int kMode = kSpin>
 __device__ __forceinline__ void wait(WaitContext* w, uint64_t* bar, uint32_t parity, int where) {
   if (mbar_try_wait(bar, parity)) return;
-  wait_slow<kSleepNs>(w, bar, parity, where);
+  wait_slow<kMode>(w, bar, parity, where);
 }
 
 // Wait that ignores the abort flag (used while unwinding: copies and MMAs already in flight
@@ -58,11 +67,7 @@ __device__ __forceinline__ void wait(WaitContext* w, uint64_t* bar, uint32_t par
 __device__ __noinline__ bool drain_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
-#pragma unroll 1
-    for (int k = 0; k < 32; ++k) {
-      if (mbar_try_wait(bar, parity)) return true;
-      asm volatile("nanosleep.u32 64;");
-    }
+    if (mbar_try_wait_hint(bar, parity, kParkNs)) return true;
     if (globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
