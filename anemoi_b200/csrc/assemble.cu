@@ -197,3 +197,18 @@ extern "C" int anemoi_sm100_merge_heads(const void* recv, void* out, int64_t row
   return anemoi_sm100_merge_heads_into(recv, out, rows, ranks, heads_per_rank, head_dim,
                                        heads_per_rank, 0, stream);
 }
+
+// One strided copy between pinned host memory and the device: `height` rows of `width` bytes,
+// rows `src_pitch` / `dst_pitch` bytes apart (cudaMemcpy2DAsync).  With it a group of heads of
+// a host tensor [1, S, H, D] moves to or from a contiguous device tensor [1, S, heads, D] in one
+// call, so that the copies of one head group can run under the attention of another.
+extern "C" int anemoi_sm100_copy_rows(void* dst, int64_t dst_pitch, const void* src,
+                                      int64_t src_pitch, int64_t width, int64_t height,
+                                      int32_t to_device, void* stream) {
+  if (!dst || !src || width <= 0 || height <= 0 || dst_pitch < width || src_pitch < width)
+    return ANEMOI_SM100_EINVAL;
+  const cudaError_t err = cudaMemcpy2DAsync(
+      dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width, (size_t)height,
+      to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  return err == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}

@@ -24,6 +24,19 @@ LIBRARY_NAME = "libanemoi_sm100.so"
 
 ERRORS = {-1: "invalid argument", -2: "CUDA launch failure", -3: "size beyond a documented limit"}
 
+# Kernels of this library launched so far by the calling process, per entry point (each wrapper
+# below adds what its entry launches; memset nodes are not kernels).  Benchmarks read the
+# difference over their timed region.
+LAUNCHES: dict[str, int] = {}
+
+
+def _count(name: str, kernels: int) -> None:
+    LAUNCHES[name] = LAUNCHES.get(name, 0) + kernels
+
+
+def launches_total() -> int:
+    return sum(LAUNCHES.values())
+
 
 class Shape(C.Structure):
     _fields_ = [
@@ -80,6 +93,7 @@ def library() -> C.CDLL:
         "anemoi_sm100_route_static": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, P, I64, P]),
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
         "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
+        "anemoi_sm100_copy_rows": (C.c_int, [P, I64, P, I64, I64, I64, I32, P]),
         "anemoi_sm100_set_wait_limit_ns": (C.c_int, [C.c_uint64]),
         "anemoi_sm100_wait_selftest": (C.c_int, [C.c_uint64, P, P]),
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
@@ -109,7 +123,7 @@ EXPORTED = (
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
     "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
-    "anemoi_sm100_wait_selftest",
+    "anemoi_sm100_wait_selftest", "anemoi_sm100_copy_rows",
 )
 
 
@@ -182,6 +196,7 @@ def allocate_operands(shape: Shape, device) -> OperandStore:
 def prepare(shape: Shape, q, k, v, indices, counts, store: OperandStore) -> None:
     """Fill the operand store from raw ``[1, S, H, D]`` Q/K/V views (see anemoi_sm100_prepare)."""
     strides = (C.c_int64 * 6)(q.stride(1), q.stride(2), k.stride(1), k.stride(2), v.stride(1), v.stride(2))
+    _count("prepare", 2 if shape.has_int8 else 1)      # V amax pre-pass + the fused pass
     _check(library().anemoi_sm100_prepare(C.byref(shape), _ptr(q), _ptr(k), _ptr(v), strides,
                                           _ptr(indices), _ptr(counts), C.byref(store.struct),
                                           _stream(q.device)), "anemoi_sm100_prepare")
@@ -191,6 +206,7 @@ def draft_probability(shape: Shape, store: OperandStore, maxpool_weight: float) 
     r = shape.video_blocks
     prob = torch.empty((shape.heads, r, r), dtype=torch.float16, device=store.buffers["q_pool"].device)
     b = store.buffers
+    _count("draft_probability", 1)
     _check(library().anemoi_sm100_draft_probability(
         C.byref(shape), _ptr(b["q_pool"]), _ptr(b["k_pool"]), _ptr(b["q_max_pool"]),
         _ptr(b["k_max_pool"]), float(maxpool_weight), _ptr(prob), _stream(prob.device)),
@@ -221,6 +237,7 @@ def route(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_p
         stage_ids=torch.empty((h, max(cap, 1)), dtype=torch.int32, device=dev),
         capacity=max(cap, 1),
     )
+    _count("route", 5)                                  # hist, threshold, tally, emit, order
     _check(lib.anemoi_sm100_route(C.byref(shape), _ptr(prob), n16, n8, n4, prefix_phase,
                                   _ptr(scratch), scratch.numel(), _ptr(lists.row_offset),
                                   _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,
@@ -248,6 +265,7 @@ def attention(shape: Shape, store: OperandStore, lists: RouteLists, valid_k: tor
     dev = valid_k.device
     out = torch.empty((shape.heads, shape.video_blocks * shape.query_block, shape.head_dim),
                       dtype=torch.float16, device=dev)
+    _count("attention", 1)
     _check(library().anemoi_sm100_attention(
         C.byref(shape), C.byref(store.struct), _ptr(lists.row_offset), _ptr(lists.row_counts),
         _ptr(lists.stage_ids), lists.capacity, _ptr(valid_k), _ptr(out), _ptr(status),
@@ -260,10 +278,33 @@ def prefix_attention(shape: Shape, store: OperandStore, valid_k: torch.Tensor,
     dev = valid_k.device
     rows = shape.prefix_query_tiles * shape.query_block
     out = torch.empty((shape.heads, rows, shape.head_dim), dtype=torch.float16, device=dev)
+    _count("prefix_attention", 1)
     _check(library().anemoi_sm100_prefix_attention(
         C.byref(shape), C.byref(store.struct), _ptr(valid_k), _ptr(out), _ptr(status),
         _stream(dev)), "anemoi_sm100_prefix_attention")
     return out
+
+
+def copy_head_group(dst: torch.Tensor, src: torch.Tensor, stream: torch.cuda.Stream) -> None:
+    """One strided copy of a head group between a pinned host tensor and a device tensor.
+
+    ``dst`` and ``src`` are ``[1, S, heads, D]`` views with the same shape, contiguous in their
+    last two dimensions; exactly one of them is on the device.  Asynchronous on ``stream``."""
+    if dst.shape != src.shape or dst.dtype != src.dtype or dst.ndim != 4 or dst.size(0) != 1:
+        raise ValueError("copy_head_group needs two [1, S, heads, D] views of one dtype")
+    for t in (dst, src):
+        if t.stride(3) != 1 or t.stride(2) != t.size(3):
+            raise ValueError("copy_head_group needs views contiguous over (heads, D)")
+        if t.device.type == "cpu" and not t.is_pinned():
+            raise ValueError("the host side of copy_head_group must be pinned memory")
+    to_device = dst.device.type == "cuda"
+    if to_device == (src.device.type == "cuda"):
+        raise ValueError("copy_head_group copies between the host and the device")
+    size = dst.element_size()
+    _check(library().anemoi_sm100_copy_rows(
+        _ptr(dst), dst.stride(1) * size, _ptr(src), src.stride(1) * size,
+        dst.size(2) * dst.size(3) * size, dst.size(1), int(to_device),
+        C.c_void_p(stream.cuda_stream)), "anemoi_sm100_copy_rows")
 
 
 def set_wait_limit_ns(limit_ns: int) -> None:
@@ -288,6 +329,7 @@ def assemble(shape: Shape, prefix_out: torch.Tensor | None, out_packed: torch.Te
         if prefix_out.dtype not in (torch.float16, dtype):
             raise TypeError("prefix rows must be fp16 or the caller's dtype")
         caller = int(prefix_out.dtype != torch.float16)
+    _count("assemble", 1)
     _check(library().anemoi_sm100_assemble(
         C.byref(shape), _ptr(prefix_out), rows, caller, _ptr(out_packed), _ptr(inverse),
         _ptr(row_counts), _ptr(out), _stream(dev)), "anemoi_sm100_assemble")
@@ -314,6 +356,7 @@ def pack_qkv_destination_major(q, k, v, world: int, head_begin: int = 0,
     if out.numel() == 0:
         return out
     strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
+    _count("pack_qkv", 1)
     _check(library().anemoi_sm100_pack_qkv_heads(_ptr(q), _ptr(k), _ptr(v), _ptr(out), rows, heads, d,
                                                  world, head_begin, head_count, strides,
                                                  _stream(q.device)),
@@ -339,6 +382,7 @@ def merge_heads(x: torch.Tensor, out: torch.Tensor | None = None, head_begin: in
         raise ValueError("head range outside the heads of a rank")
     if x.numel() == 0:
         return out
+    _count("merge_heads", 1)
     _check(library().anemoi_sm100_merge_heads_into(_ptr(x), _ptr(out), rows, world, hc, d, per_rank,
                                                    head_begin, _stream(x.device)),
            "anemoi_sm100_merge_heads_into")

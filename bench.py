@@ -201,6 +201,94 @@ def cpu_sample(w, query_blocks: int, seed: int = 1) -> dict:
     }
 
 
+def reference_kernels_same_gpu(heads: int = 56, repeats: int = 5) -> dict:
+    """The reference's OWN kernels (its SM120 extension built unchanged for sm_100a,
+    oracle/ref_build) beside this library's on the same B200, stage by stage, on the second
+    benchmark configuration (prefix 512 + 21x30x52, Q128, max-pool 0.5, INT8/FP16 50/50): the
+    largest configuration whose cells the reference's kernels can run on sm_100a (its NVFP4
+    phase does not assemble for this architecture).  Driven as the reference's executor drives
+    them (anemoi/layers/attention/mpa/executor.py:1013-1199)."""
+    import numpy as np
+
+    from anemoi_b200 import executor
+    from anemoi_b200.layout import materialize_ragged_2d_layout
+    from anemoi_b200.routing import route_counts
+    from tests.golden.make_kernel_golden import load_reference_ops
+
+    ops = load_reference_ops()
+    w = dict(WORKLOAD, video=(21, 30, 52), heads=heads, ratios=(0.0, 0.5, 0.5), maxpool=0.5)
+    device = torch.device("cuda", 0)
+    q, k, v = synth_qkv(w, heads, device, seed=0)
+    prefix, qb, dim, video = w["prefix"], w["query_block"], w["dim"], w["video"]
+    lay = materialize_ragged_2d_layout(device, frames=video[0], height=video[1], width=video[2],
+                                       logical_block=qb)
+    counts = lay.counts
+    valid = torch.arange(qb, device=device).view(1, -1) < counts.view(-1, 1)
+    indices, slot_valid = lay.indices.to(torch.int64), valid.reshape(-1)
+    blocks, pb = counts.numel(), math.ceil(prefix / 64)
+    pre = torch.clamp(prefix - torch.arange(pb, device=device, dtype=torch.int32) * 64, 0, 64)
+    vid = torch.stack((counts.clamp_max(64), (counts - 64).clamp_min(0)), dim=-1).reshape(-1)
+    valid_k = torch.cat((pre, vid)).to(torch.int32).view(1, -1).contiguous()
+    n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=w["drop"], nvfp4_ratio=0.0,
+                               int8_ratio=0.5, fp16_ratio=0.5)
+    scale = 1.0 / math.sqrt(dim)
+
+    def mark():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def reference_layer(book):
+        t = [mark()]
+        p = ops.prepare_h3_sm120_operands(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                          indices, slot_valid, counts, prefix, qb, False, True, False, True,
+                                          True, True, None, None, None)
+        t.append(mark())
+        prob = ops.sm120_h3_draft_probability(p[0], p[1], p[25], p[26], 0.5)
+        ids, low, mid, high = ops.sm120_h3_route_precision(prob, n16, n8, n4, None, None, 0)
+        mids, _, mid_c, hi_c = ops.sm120_h3_materialize_route(ids, low, mid, high, qb, pb, 1, True, True)
+        t.append(mark())
+        ops.sm120_q128_int8_attention_forward(p[17], p[19], p[21], p[2], p[3], p[4], mids, mid_c, hi_c,
+                                              p[18], p[20], p[22], valid_k, 0, scale, True)
+        t.append(mark())
+        ops.sm120_q128_prefix_int8_attention_forward(p[23], p[19], p[21], p[24], p[20], p[22], valid_k,
+                                                     prefix, scale)
+        t.append(mark())
+        book.append(t)
+
+    for _ in range(2):
+        reference_layer([])
+    torch.cuda.synchronize()
+    book = []
+    for _ in range(repeats):
+        reference_layer(book)
+    torch.cuda.synchronize()
+    names = ("prepare", "draft+route+materialise", "attention int8+fp16", "prefix rows int8")
+    ref = {n: float(np.median([t[i].elapsed_time(t[i + 1]) for t in book])) for i, n in enumerate(names)}
+    kw = dict(prefix_tokens=prefix, sparsity_ratio=w["drop"], retained_nvfp4_ratio=0.0,
+              retained_int8_ratio=0.5, retained_fp16_ratio=0.5, video_shape=video, layer=0,
+              query_block_size=qb, maxpool_weight=0.5)
+    for _ in range(2):
+        executor.sm100_ragged_attention(q, k, v, **kw)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    executor.collect_stage_events(True)
+    start.record()
+    for _ in range(repeats):
+        executor.sm100_ragged_attention(q, k, v, **kw)
+    end.record()
+    mine = {kk: vv / repeats for kk, vv in executor.stage_times_ms().items()}
+    executor.collect_stage_events(False)
+    return {"workload": "configs[1]: prefix 512 + video 21x30x52 (S=33272), H=56, D=128, bf16, Q128, 80% drop, "
+                        "max-pool 0.5, INT8/FP16 50/50",
+            "reference_kernels_ms": {**{kk: round(vv, 3) for kk, vv in ref.items()},
+                                     "sum (no output assembly)": round(sum(ref.values()), 3)},
+            "this_library_ms": {**{kk: round(vv, 3) for kk, vv in mine.items()},
+                                "whole layer": round(start.elapsed_time(end) / repeats, 3)},
+            "note": "reference = its mma.sync kernels recompiled for sm_100a; stage times by CUDA events; this "
+                    "library's prefix rows run on a side stream beside draft and route"}
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -208,7 +296,7 @@ def run_reference(args) -> None:
     times = []
     last = None
     for i in range(args.warmup + args.steps):
-        last = cpu_sample(WORKLOAD, query_blocks=2, seed=1 + i)
+        last = cpu_sample(WORKLOAD, query_blocks=args.cpu_query_blocks, seed=1 + i)
         if i >= args.warmup:
             times.append(last["layer_seconds"])
     mean_s = sum(times) / len(times)
@@ -221,10 +309,16 @@ def run_reference(args) -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s dense-equivalent", "cores": last["cores"],
-                         "kind": "port", "sample": last["sample"]},
+                         "kind": "port", "extrapolated": True, "sample": last["sample"]},
         "e2e": {"value": value, "unit": "TFLOP/s dense-equivalent", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
+    # Beside the CPU port: the reference's own CUDA kernels on this GPU, where they were built.
+    if torch.cuda.is_available() and (ROOT / "oracle" / "_ref" / "_ref_sm120.so").exists():
+        try:
+            line["reference_kernels_b200"] = reference_kernels_same_gpu()
+        except Exception as exc:  # the comparison is extra information, never a reason to fail the arm
+            line["reference_kernels_b200"] = {"unavailable": str(exc).splitlines()[0][:160]}
     print(json.dumps(line))
 
 
@@ -235,6 +329,43 @@ def workload_config(n_gpus: int) -> dict:
             "parallelism": f"ulysses{n_gpus}" if n_gpus > 1 else "single",
             "heads_per_gpu": w["heads"] // n_gpus,
             "l2": "inputs (3.66 GB of Q/K/V) exceed the 126 MB L2; no explicit flush"}
+
+
+def profiled_traffic(heads_local: int, s_total: int):
+    """DRAM bytes of one video-attention launch from profiles/attention_kernel_small_case.md
+    (a line ``dram_bytes_small_case: <read> <written> heads=<h> tokens=<s>``), scaled by heads x tokens."""
+    path = ROOT / "profiles" / "attention_kernel_small_case.md"
+    try:
+        for text in path.read_text().splitlines():
+            if text.startswith("dram_bytes_small_case:"):
+                fields = text.split()
+                read, written = float(fields[1]), float(fields[2])
+                meta = dict(f.split("=") for f in fields[3:])
+                scale = heads_local * s_total / (int(meta["heads"]) * int(meta["tokens"]))
+                return (read + written) * scale, (
+                    f"ncu dram__bytes of the small case in {path.name} ({meta['heads']} heads, "
+                    f"{meta['tokens']} tokens), scaled by heads x tokens")
+    except (OSError, ValueError, KeyError, IndexError):
+        pass
+    return None, "no ncu figure in profiles/attention_kernel_small_case.md"
+
+
+def error_versus_dense(q, k, v, out, head: int = 0, rows: int = 2048) -> dict:
+    """Error of the sparse mixed-precision layer against dense fp32 attention of the same inputs
+    on `rows` evenly spaced query rows of one head (sparsity and quantisation error together)."""
+    s_total, d = q.shape[1], q.shape[3]
+    pick = torch.linspace(0, s_total - 1, rows, device=q.device).long()
+    qf = q[0, pick, head].float()
+    kf, vf = k[0, :, head].float(), v[0, :, head].float()
+    dense = torch.softmax(qf @ kf.T / math.sqrt(d), dim=-1) @ vf
+    got = out[0, pick, head].float()
+    diff = got - dense
+    return {"head": head, "rows": rows, "max_abs": float(diff.abs().max()),
+            "relative_l2": float(diff.norm() / dense.norm()),
+            "cosine": float(torch.nn.functional.cosine_similarity(got.flatten(), dense.flatten(), dim=0)),
+            "note": "error of the ALGORITHM at 80% block drop on this synthetic data (Q and K are independent "
+                    "random fields, so block-mean routing finds little of the attention mass); the CUDA path "
+                    "matches the CPU oracle on the same inputs within 2e-2 / cosine 0.999 (tests)"}
 
 
 def dense_flash_sample(q, k, v, heads: int = 8) -> dict:
@@ -330,8 +461,11 @@ def run_ours(args) -> None:
         raise SystemExit("attention kernel reported an aborted wait")
 
     # ---- timed: inputs resident in HBM ----
+    from anemoi_b200 import native
+
     executor.collect_stage_events(True)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = native.launches_total()
     with ClockSampler(local) as clocks:
         barrier()
         start.record()
@@ -340,6 +474,7 @@ def run_ours(args) -> None:
         end.record()
         barrier()
     ms = start.elapsed_time(end) / args.steps
+    launches = (native.launches_total() - launches_before) // args.steps
     stages = {kk: vv / args.steps for kk, vv in executor.stage_times_ms().items()}
     executor.collect_stage_events(False)
     t = torch.tensor([ms], device=device)
@@ -350,10 +485,20 @@ def run_ours(args) -> None:
     # ---- timed: end to end from pinned host memory ----
     hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
     hout = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+    if world == 1:
+        # the library's host-input entry: head groups on three streams, so that the copy of one
+        # group runs under the layer of another (heads are independent; same result bit for bit)
+        from anemoi_b200 import HostAttention
 
-    def e2e_step():
-        dq, dk, dv = (x.to(device, non_blocking=True) for x in (hq, hk, hv))
-        hout.copy_(layer(dq, dk, dv), non_blocking=True)
+        host_call = HostAttention(device, group_heads=args.e2e_group_heads)
+
+        def e2e_step():
+            host_call(hq, hk, hv, hout, layout=layout, layer=0, sparse_config=sparse,
+                      quant_config=quant, calibration=calib)
+    else:
+        def e2e_step():
+            dq, dk, dv = (x.to(device, non_blocking=True) for x in (hq, hk, hv))
+            hout.copy_(layer(dq, dk, dv), non_blocking=True)
 
     for _ in range(min(args.warmup, 2)):
         e2e_step()
@@ -368,6 +513,22 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item())
+    e2e_matches = bool(torch.equal(hout.to(device), out)) if world == 1 else None
+
+    # ---- N > 1: the sharded result against an unsharded run of one head (outside the timing) ----
+    sharded_ok = None
+    if world > 1:
+        head = 0
+        parts = [torch.empty(r, w["dim"], dtype=q.dtype, device=device) for r in rows]
+        full = []
+        for t in (q, k, v):
+            dist.all_gather(parts, t[0, :, head].contiguous())
+            full.append(torch.cat(parts).view(1, s_total, 1, w["dim"]).clone())
+        if rank == 0:
+            single = anemoi_attention(*full, layout=layout, layer=0, sparse_config=sparse,
+                                      quant_config=quant, calibration=calib)
+            sharded_ok = bool(torch.equal(single[0, lo : lo + rows[rank], 0], out[0, :, head]))
+        del full, parts
 
     if rank == 0:
         from anemoi_b200.layout import materialize_ragged_2d_layout
@@ -390,11 +551,11 @@ def run_ours(args) -> None:
         mixed_peak = (f4 + f8 + f16) / (f4 / (4 * bf16) + f8 / (2 * bf16) + f16 / bf16)
         attn_ms = stages.get("attention", float("nan"))
         achieved = video_flops / (attn_ms * 1e-3) / 1e12 if attn_ms == attn_ms else None
-        # DRAM traffic of one video-attention launch: the ncu capture of the small profiling case
-        # (--profile-case: 305.6 MB read + 71.3 MB written for 8 heads of 33,272 tokens) scaled by
-        # heads x tokens; the operands of a head stay L2-resident in both
-        # cases, so the traffic is the compulsory read of the records and the write of O.
-        traffic = (305.575168e6 + 71.335680e6) / (8 * 33272) * heads_local * s_total
+        # DRAM traffic of one video-attention launch: read from the committed ncu summary of the
+        # small profiling case (8 heads of 33,272 tokens) and scaled by heads x tokens; the
+        # operands of a head stay L2-resident in both cases, so the traffic is the compulsory
+        # read of the records and the write of O.  None when the summary does not carry it.
+        traffic, traffic_source = profiled_traffic(heads_local, s_total)
         line = {
             "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -405,17 +566,20 @@ def run_ours(args) -> None:
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s dense-equivalent",
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in (q, k, v))),
-                    "d2h_bytes_per_step": int(out.numel() * out.element_size())},
-            # 11 library kernels per attention call (v_amax, prepare, prefix attention, draft, hist,
-            # threshold, tally, emit, order, attention, assemble); with N > 1 every head group adds
-            # its pack and merge kernel
-            "gpu_launches": 11 if world == 1 else 13 * len(ulysses.head_groups(w["heads"] // world,
-                                                                               args.pipeline_groups)),
+                    "d2h_bytes_per_step": int(out.numel() * out.element_size()),
+                    "path": (f"HostAttention: head groups of {args.e2e_group_heads} on three streams, one strided "
+                             "copy per group and tensor" if world == 1 else
+                             "per rank: copy in its sequence shard, Ulysses layer, copy out"),
+                    "equals_device_resident_result": e2e_matches},
+            # kernels of this library launched per step, counted by the ctypes layer as it calls them
+            # (v_amax, prepare, prefix attention, draft, hist, threshold, tally, emit, order,
+            # attention, assemble; with N > 1 also pack and merge)
+            "gpu_launches": launches,
             "stage_ms": stages,
             "roofline": {"bound": "tensor", "kernel": "attention_kernel<128> (video query blocks)",
                          "achieved": achieved, "peak": mixed_peak, "unit": "TFLOP/s",
                          "frac": (achieved / mixed_peak) if achieved else None, "traffic": traffic,
-                         "traffic_source": "ncu dram bytes of the 8-head S=33,272 case, scaled by heads x tokens",
+                         "traffic_source": traffic_source,
                          "peak_source": f"{peak_kind} bf16 GEMM {bf16} TFLOP/s x (1, 2, 4) for fp16, 8-bit, NVFP4 "
                                         "cells, weighted by executed FLOPs"},
         }
@@ -431,12 +595,16 @@ def run_ours(args) -> None:
                 "frac_of_mixed": (achieved / measured_mixed) if achieved else None,
                 "note": "TFLOP/s of the library's tensor-pipe probe per kind; mixed = executed FLOPs weighted "
                         "(QK of the 8-bit cell is kind::i8, its PV kind::f8f6f4)"}
+        if world > 1:
+            line["sharded_equals_single"] = sharded_ok
         if world == 1 and not args.no_dense:
             line["dense_bf16"] = dense_flash_sample(q, k, v)
+            line["error_vs_dense_fp32"] = error_versus_dense(q, k, v, out)
         if world == 1 and not args.no_cpu_baseline:
-            cpu = cpu_sample(w, query_blocks=3)
+            cpu = cpu_sample(w, query_blocks=args.cpu_query_blocks)
             line["cpu_baseline"] = {"value": cpu["tflops"], "unit": "TFLOP/s dense-equivalent",
-                                    "cores": cpu["cores"], "kind": "port", "sample": cpu["sample"]}
+                                    "cores": cpu["cores"], "kind": "port", "extrapolated": True,
+                                    "sample": cpu["sample"]}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -531,8 +699,12 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-query-blocks", type=int, default=32,
+                    help="query blocks of attention timed per CPU sample (evenly spaced over the video)")
     ap.add_argument("--no-dense", action="store_true",
                     help="skip the dense bf16 library attention timed beside the sparse layer")
+    ap.add_argument("--e2e-group-heads", type=int, default=8,
+                    help="heads per group of the pipelined host-input call (end-to-end number)")
     ap.add_argument("--pipeline-groups", type=int, default=1,
                     help="head groups whose exchange is pipelined under the attention (N > 1)")
     ap.add_argument("--sweep", action="store_true", help="run the kernel sweep instead of the benchmark")

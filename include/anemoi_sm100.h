@@ -224,6 +224,14 @@ int anemoi_sm100_merge_heads_into(const void* recv, void* out, int64_t rows, int
                                   int32_t head_count, int32_t head_dim, int32_t heads_per_rank,
                                   int32_t head_begin, void* stream);
 
+/* One strided copy between pinned host memory and the device (rows of `width` bytes, `height`
+ * of them, pitches in bytes): a group of heads of a host [1,S,H,D] tensor to or from a
+ * contiguous device [1,S,heads,D] tensor.  Used by the host-input entry of the Python layer to
+ * overlap the copies of one head group with the attention of another; the reference has no
+ * host-input path (its tensors are CUDA tensors, anemoi/layers/attention/api.py:134-194). */
+int anemoi_sm100_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
+                           int64_t width, int64_t height, int32_t to_device, void* stream);
+
 /* Producer fusion in front of the attention path: per-head RMS norm with weight, then partial
  * rotary embedding, in place on Q or K.  x [tokens][heads][head_dim] 16-bit (strides[2] = token and
  * head stride in elements, multiples of 8; head_dim contiguous), weight [head_dim] in x's type,

@@ -81,3 +81,23 @@ def test_route_runs_on_every_visible_device(native_library):
             outs.append(out.cpu())
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
+
+
+def test_pipelined_host_input_equals_the_single_call(native_library):
+    """Q/K/V in pinned host memory, walked in head groups on three streams (copy in, layer, copy
+    out): heads are independent, so the result equals one call on all heads bit for bit."""
+    from anemoi_b200 import HostAttention, NVFP4Calibration, QuantConfig, SparseConfig, VisualLayout, anemoi_attention
+
+    vs, prefix, heads = (2, 12, 20), 37, 5
+    q, k, v = smooth_fields(*vs, heads, 128, prefix, seed=4, outliers=(17, 93), dtype=torch.bfloat16)
+    kw = dict(layout=VisualLayout(vs, prefix), layer=0, sparse_config=SparseConfig(128, 0.6, (), 0.5),
+              quant_config=QuantConfig(0.4, 0.4, 0.2), calibration=NVFP4Calibration(0.01, 0.01, 0.002))
+    want = anemoi_attention(q.cuda(), k.cuda(), v.cuda(), **kw).cpu()
+    hq, hk, hv = (t.contiguous().pin_memory() for t in (q, k, v))
+    hout = torch.empty_like(hq).pin_memory()
+    runner = HostAttention("cuda", group_heads=2)       # groups of 2, 2 and 1 heads
+    for _ in range(2):                                   # second pass reuses the device buffers
+        hout.fill_(float("nan"))
+        runner(hq, hk, hv, hout, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(hout, want)
