@@ -612,6 +612,135 @@ def run_ours(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------
+# one denoising step of a random-init MiniMax-H3-shaped block stack (the fifth configuration)
+# ------------------------------------------------------------------------------------------
+def run_dit_step(args) -> None:
+    """`--config dit-step`: one denoising step of the stand-in block stack
+    (anemoi_b200/h3_stack.py: 50 blocks, width 5,376, 56 x 128 heads) on the 512 + 21x48x84-token
+    sequence, sequence-sharded over N GPUs with the Ulysses exchange around every attention and
+    `H3MPAAttention` behind it (dense for the first two layers, NVFP4/INT8/FP16 40/40/20 at 80 %
+    drop elsewhere).  One JSON line: step time, time inside exchange + attention, its share.
+    Not the headline line: `metric` names the step."""
+    import torch.distributed as dist
+
+    from anemoi_b200 import ulysses
+    from anemoi_b200.adapter import H3MPAAttention, H3MPAConfig
+    from anemoi_b200.build import build
+    from anemoi_b200.h3_stack import H3BlockStack, H3StackConfig
+    from anemoi_b200.producer import fused_qknorm_rope
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if rank == 0:
+        build()
+    if world > 1:
+        dist.barrier()
+
+    w = WORKLOAD
+    cfg = H3StackConfig(layers=args.dit_layers)
+    s_total = w["prefix"] + math.prod(w["video"])
+    rows = ulysses.shard_rows(s_total, world)
+    lo = sum(rows[:rank])
+    stack = H3BlockStack(cfg, device, seed=0)
+    gen = torch.Generator(device=device).manual_seed(100 + rank)
+    x = torch.randn(rows[rank], cfg.width, generator=gen, device=device).to(torch.bfloat16)
+    pos = torch.arange(lo, lo + rows[rank], device=device, dtype=torch.float32)
+    freq = torch.exp(-torch.arange(cfg.rotary_dim // 2, device=device, dtype=torch.float32) * (8.0 / cfg.rotary_dim))
+    ang = torch.cat((pos[:, None] * freq[None], pos[:, None] * freq[None]), dim=-1)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+
+    # per-layer NVFP4 tensor scales = amax / (6 * 448) of the layer's Q, K, V, from a calibration
+    # pass whose attention just returns V (the activations of the real step differ slightly)
+    amax = torch.zeros(cfg.layers, 3, device=device)
+    layer_box = [0]
+
+    def calibrate(q, k, v):
+        amax[layer_box[0]] = torch.stack([t.float().abs().max() for t in (q, k, v)])
+        layer_box[0] += 1
+        return v
+
+    stack.step(x, cos, sin, calibrate, norm_rope=fused_qknorm_rope)
+    if world > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+    scales = (amax / (6 * 448)).clamp_min(1e-8).cpu().tolist()
+    attention = H3MPAAttention(
+        H3MPAConfig(video_shape=w["video"], prefix_tokens=w["prefix"], sparsity_ratio=w["drop"],
+                    query_block_size=w["query_block"], nvfp4_ratio=w["ratios"][0], int8_ratio=w["ratios"][1],
+                    fp16_ratio=w["ratios"][2], dense_first_steps=0, dense_first_layers=args.dit_dense_layers,
+                    layers_per_step=cfg.layers),
+        nvfp4_scales={"scales": {"q_tensor_scale": [r[0] for r in scales],
+                                 "k_tensor_scale": [r[1] for r in scales],
+                                 "v_tensor_scale": [r[2] for r in scales]}})
+    position_ids = torch.empty(s_total, device="meta")
+    marks = []
+
+    def on_attention(begin):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        marks.append(e)
+
+    def one_step(timestep: float):
+        attention.observe(timestep=torch.tensor(timestep), video_indices=None, position_ids=position_ids)
+        return stack.step(x, cos, sin, attention, norm_rope=fused_qknorm_rope, on_attention=on_attention)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from anemoi_b200 import executor
+
+    t = 1.0
+    for _ in range(args.warmup):
+        one_step(t)
+        t -= 0.02
+    barrier()
+    marks.clear()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            out = one_step(t)
+            t -= 0.02
+        end.record()
+        barrier()
+    if executor.last_status(device) != 0:
+        raise SystemExit("attention kernel reported an aborted wait")
+    step_ms = start.elapsed_time(end) / args.steps
+    attn_ms = sum(a.elapsed_time(b) for a, b in zip(marks[0::2], marks[1::2])) / args.steps
+    both = torch.tensor([step_ms, attn_ms], device=device)
+    if world > 1:
+        dist.all_reduce(both, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        stats = attention.stats()
+        print(json.dumps({
+            "metric": "one denoising step of a random-init MiniMax-H3-shaped block stack, ms", "value": float(both[0]),
+            "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": False,
+            "scaling": "strong", "data": "synthetic", "dtype": "bf16 GEMMs; nvfp4+int8/e4m3+fp16 attention",
+            "attention_and_exchange_ms": float(both[1]), "attention_share": float(both[1] / both[0]),
+            "finite": bool(torch.isfinite(out).all()),
+            "config": {"workload": "configs[4] stand-in: 512-token prefix + 21x48x84 video tokens, "
+                                   f"{cfg.layers} blocks (width {cfg.width}, {cfg.heads}x{cfg.head_dim} heads, "
+                                   f"SwiGLU {cfg.ffn_width} assumed, {cfg.rotary_dim} rotary channels assumed), "
+                                   f"dense attention in the first {args.dit_dense_layers} layers, sparse "
+                                   "NVFP4/INT8/FP16 40/40/20 at 80% drop elsewhere",
+                       "parallelism": f"ulysses{world}" if world > 1 else "single",
+                       "dense_calls": stats["dense_calls"], "mpa_calls": stats["mpa_calls"]},
+            "clocks": clocks.summary()}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
 # kernel sweep (the fourth benchmark configuration): not a bench line, a table
 # ------------------------------------------------------------------------------------------
 SWEEP_CELLS = {"nvfp4": (1.0, 0.0, 0.0), "int8": (0.0, 1.0, 0.0), "fp16": (0.0, 0.0, 1.0),
@@ -707,6 +836,11 @@ def main() -> None:
                     help="heads per group of the pipelined host-input call (end-to-end number)")
     ap.add_argument("--pipeline-groups", type=int, default=1,
                     help="head groups whose exchange is pipelined under the attention (N > 1)")
+    ap.add_argument("--config", choices=("layer", "dit-step"), default="layer",
+                    help="layer: the headline attention-layer benchmark; dit-step: one denoising step of the "
+                         "random-init block stack with Ulysses (not the headline line)")
+    ap.add_argument("--dit-layers", type=int, default=50)
+    ap.add_argument("--dit-dense-layers", type=int, default=2)
     ap.add_argument("--sweep", action="store_true", help="run the kernel sweep instead of the benchmark")
     ap.add_argument("--sweep-heads", type=int, default=4)
     ap.add_argument("--sweep-out", default="")
@@ -717,6 +851,8 @@ def main() -> None:
         WORKLOAD.update(PROFILE_WORKLOAD)
     if args.sweep:
         run_sweep(args)
+    elif args.config == "dit-step":
+        run_dit_step(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -96,3 +96,55 @@ def test_head_groups_cover_the_local_heads():
         parts = ulysses.head_groups(heads, groups)
         assert parts[0][0] == 0 and sum(c for _, c in parts) == heads
         assert all(parts[i][0] + parts[i][1] == parts[i + 1][0] for i in range(len(parts) - 1))
+
+
+def _stack_worker(rank, world, port, results):
+    """The stand-in block stack on two CPU ranks: sequence-sharded with the exchange around the
+    attention equals the unsharded stack (fp32, tiny widths, eager stand-ins for the CUDA kernels)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from anemoi_b200.h3_stack import H3BlockStack, H3StackConfig
+        from oracle.producer import eager_reference
+
+        cfg = H3StackConfig(width=48, heads=4, head_dim=16, ffn_width=64, rotary_dim=16, layers=3)
+        stack = H3BlockStack(cfg, "cpu", dtype=torch.float32, seed=3)
+        total = 37
+        gen = torch.Generator().manual_seed(9)
+        x = torch.randn(total, cfg.width, generator=gen)
+        ang = torch.randn(total, cfg.rotary_dim, generator=gen)
+        cos, sin = ang.cos(), ang.sin()
+
+        def norm_rope(t, weight, c, s_, eps):
+            t.copy_(eager_reference(t[0], weight, c, s_, eps).unsqueeze(0))
+            return t
+
+        def attention(q, k, v):      # [S, h, D] per-head dense attention
+            p = torch.softmax(torch.einsum("shd,thd->hst", q, k) / q.size(-1) ** 0.5, dim=-1)
+            return torch.einsum("hst,thd->shd", p, v)
+
+        rows = ulysses.shard_rows(total, world)
+        lo = sum(rows[:rank])
+        sl = slice(lo, lo + rows[rank])
+        ulysses.reset_row_counts()
+        got = stack.step(x[sl], cos[sl], sin[sl], attention, norm_rope=norm_rope, pack=torch_pack, merge=torch_merge)
+        # unsharded: same code with a one-rank "exchange"
+        want = _single_rank_step(stack, x, cos, sin, attention, norm_rope)
+        results[rank] = bool(torch.allclose(got, want[sl], atol=1e-5, rtol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def _single_rank_step(stack, x, cos, sin, attention, norm_rope):
+    import unittest.mock as mock
+
+    with mock.patch.object(dist, "is_initialized", lambda: False):
+        return stack.step(x, cos, sin, attention, norm_rope=norm_rope)
+
+
+def test_block_stack_sharded_equals_unsharded():
+    world = 2
+    port = _free_port()
+    results = mp.Manager().dict()
+    mp.spawn(_stack_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
