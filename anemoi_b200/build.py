@@ -10,7 +10,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libanemoi_sm100.so"
-SOURCES = ("prepare.cu", "draft.cu", "route.cu", "attention.cu", "assemble.cu", "peaks.cu", "producer.cu")
+SOURCES = ("prepare.cu", "draft.cu", "route.cu", "attention.cu", "assemble.cu", "peaks.cu", "producer.cu", "exchange.cu")
 FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

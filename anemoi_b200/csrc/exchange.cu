@@ -1,0 +1,229 @@
+// Ulysses sequence<->head exchange by direct stores into the peers' memory (one node, <= 8 ranks).
+//
+// Every rank owns one exchange region (cudaMalloc, exported with a CUDA IPC handle and mapped by
+// the other ranks of the node).  The relayout kernels store each 16-byte vector straight where
+// an all-to-all would have delivered it - over NVLink for the other ranks, locally for the own
+// part - so the collective, its send buffer and the merge pass disappear.  When the last block
+// of a push has stored its part, it writes the call's epoch into a flag word of every
+// destination; the destination's next kernel in stream order is a one-warp wait on those flags.
+// Only plain st.global / ld.acquire touch peer memory: no bulk or tensor copy, no multicast.
+//
+// Every wait has a limit (%globaltimer); a wait that runs out records 70 + the late rank in
+// the device status word and returns, so the stream drains and the host can read the failure.
+//
+// This replaces pack_qkv_destination_major + all_to_all_single and all_to_all_single +
+// merge_heads of the reference's custom Ulysses path
+// (anemoi/models/minimax_h3/solengine/models/minimax_h3/optimized/ulysses_custom.py:107-165,
+// relayout.py:83-162).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/anemoi_sm100.h"
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+
+struct PeerTable {
+  uint16_t* data[kMaxRanks];   // per rank: the destination buffer as mapped into this process
+  uint32_t* flags[kMaxRanks];  // per rank: its flag words (one per source rank)
+  int64_t first[kMaxRanks + 1];  // first row of every rank's sequence shard; [ranks] = all rows
+};
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Called by every thread after its stores.  The last block to finish publishes the epoch to
+// every destination; the fences make all blocks' stores visible, system-wide, before the flag.
+__device__ __forceinline__ void publish(const PeerTable& peers, int self, int ranks, uint32_t epoch,
+                                        unsigned int* blocks_done) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = atomicAdd(blocks_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence_system();
+  if (threadIdx.x < ranks) {
+    uint32_t* flag = peers.flags[threadIdx.x] + self;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  }
+  if (threadIdx.x == 0) *blocks_done = 0;   // ready for the next launch on this stream
+}
+
+// q,k,v [rows][heads][D] of this rank's rows -> on rank `dest`: recv [all rows][heads_local][3*D]
+// at rows first[self] + row.  Consecutive threads store consecutive 16-byte vectors of one row.
+__global__ void __launch_bounds__(256) push_qkv_kernel(const uint16_t* q, const uint16_t* k,
+                                                       const uint16_t* v, PeerTable peers, int self,
+                                                       int ranks, int64_t rows, int heads_local, int d8,
+                                                       int64_t total, int64_t qs_row, int64_t qs_head,
+                                                       int64_t ks_row, int64_t ks_head,
+                                                       int64_t vs_row, int64_t vs_head,
+                                                       uint32_t epoch, unsigned int* blocks_done) {
+  const int64_t row0 = peers.first[self];
+  for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * 256) {
+    const int c8 = (int)(idx % d8);
+    int64_t t = idx / d8;
+    const int which = (int)(t % 3);
+    t /= 3;
+    const int lh = (int)(t % heads_local);
+    t /= heads_local;
+    const int64_t row = t % rows;
+    const int dest = (int)(t / rows);
+    const int gh = dest * heads_local + lh;
+    const uint16_t* src = which == 0 ? q + row * qs_row + gh * qs_head
+                        : which == 1 ? k + row * ks_row + gh * ks_head
+                                     : v + row * vs_row + gh * vs_head;
+    uint16_t* dst = peers.data[dest] +
+                    ((((row0 + row) * heads_local + lh) * 3 + which) * (int64_t)d8 + c8) * 8;
+    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src) + c8);
+  }
+  publish(peers, self, ranks, epoch, blocks_done);
+}
+
+// out_heads [all rows][heads_local][D] (this rank's heads, every row) -> on the rank that owns
+// a row: out [its rows][ranks*heads_local][D] at heads self*heads_local + (0..heads_local)
+__global__ void __launch_bounds__(256) push_out_kernel(const uint16_t* out_heads, PeerTable peers,
+                                                       int self, int ranks, int heads_local, int d8,
+                                                       int64_t total, uint32_t epoch,
+                                                       unsigned int* blocks_done) {
+  const int inner8 = heads_local * d8;
+  for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * 256) {
+    const int tail = (int)(idx % inner8);
+    const int64_t row = idx / inner8;
+    int owner = 0;
+#pragma unroll
+    for (int r = 1; r < kMaxRanks; ++r) owner += (r < ranks && row >= peers.first[r]) ? 1 : 0;
+    uint16_t* dst = peers.data[owner] +
+                    (((row - peers.first[owner]) * ranks + self) * (int64_t)inner8 + tail) * 8;
+    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(out_heads) + idx);
+  }
+  publish(peers, self, ranks, epoch, blocks_done);
+}
+
+// One warp; lane r waits until rank r's flag has reached the epoch.
+__global__ void wait_flags_kernel(const uint32_t* flags, int ranks, uint32_t epoch, uint64_t limit_ns,
+                                  int32_t* status) {
+  const int r = threadIdx.x;
+  if (r >= ranks) return;
+  if (status && *(volatile int32_t*)status != 0) return;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+    if ((int32_t)(seen - epoch) >= 0) return;
+    if (globaltimer_ns() - t0 > limit_ns) break;
+    __nanosleep(200);
+  }
+  if (status) atomicCAS(status, 0, 70 + r);
+}
+
+int fill(PeerTable& t, void* const* data, void* const* flags, const int64_t* first, int ranks) {
+  for (int r = 0; r < ranks; ++r) {
+    if (!data[r] || !flags[r] || first[r + 1] < first[r]) return ANEMOI_SM100_EINVAL;
+    t.data[r] = static_cast<uint16_t*>(data[r]);
+    t.flags[r] = static_cast<uint32_t*>(flags[r]);
+    t.first[r] = first[r];
+  }
+  t.first[ranks] = first[ranks];
+  return ANEMOI_SM100_OK;
+}
+
+}  // namespace
+
+extern "C" int anemoi_sm100_peer_alloc(int64_t bytes, void** ptr, void* handle64) {
+  if (bytes <= 0 || !ptr || !handle64) return ANEMOI_SM100_EINVAL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return ANEMOI_SM100_ELAUNCH;
+  if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess ||
+      cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), p) != cudaSuccess) {
+    cudaFree(p);
+    cudaGetLastError();
+    return ANEMOI_SM100_ELAUNCH;
+  }
+  cudaDeviceSynchronize();
+  *ptr = p;
+  return ANEMOI_SM100_OK;
+}
+
+extern "C" int anemoi_sm100_peer_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return ANEMOI_SM100_EINVAL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof h);
+  if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return ANEMOI_SM100_ELAUNCH;
+  }
+  return ANEMOI_SM100_OK;
+}
+
+extern "C" int anemoi_sm100_peer_close(void* ptr) {
+  if (!ptr) return ANEMOI_SM100_EINVAL;
+  return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+extern "C" int anemoi_sm100_peer_free(void* ptr) {
+  if (!ptr) return ANEMOI_SM100_EINVAL;
+  return cudaFree(ptr) == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+extern "C" int anemoi_sm100_push_qkv(const void* q, const void* k, const void* v,
+                                     void* const* peer_recv, void* const* peer_flags,
+                                     const int64_t* first_rows, int32_t self, int32_t ranks,
+                                     int32_t heads, int32_t head_dim, const int64_t* strides,
+                                     uint32_t epoch, void* blocks_done, void* stream) {
+  if (!peer_recv || !peer_flags || !first_rows || !strides || !blocks_done || ranks <= 0 || ranks > kMaxRanks || self < 0 || self >= ranks || heads <= 0 || heads % ranks ||
+      head_dim <= 0 || head_dim % 8)
+    return ANEMOI_SM100_EINVAL;
+  for (int i = 0; i < 6; ++i)
+    if (strides[i] % 8) return ANEMOI_SM100_EINVAL;
+  PeerTable t{};
+  if (int rc = fill(t, peer_recv, peer_flags, first_rows, ranks)) return rc;
+  const int64_t rows = first_rows[self + 1] - first_rows[self];
+  if (rows > 0 && (!q || !k || !v)) return ANEMOI_SM100_EINVAL;   // a rank without rows has no tensors
+  const int heads_local = heads / ranks, d8 = head_dim / 8;
+  const int64_t total = (int64_t)ranks * rows * heads_local * 3 * d8;
+  // a rank without rows still has to publish its epoch: one block, no stores
+  const int blocks = (int)max((int64_t)1, min((total + 255) / 256, (int64_t)(148 * 16)));
+  push_qkv_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(k),
+      static_cast<const uint16_t*>(v), t, self, ranks, max(rows, (int64_t)1), heads_local, d8, total,
+      strides[0], strides[1], strides[2], strides[3], strides[4], strides[5], epoch,
+      static_cast<unsigned int*>(blocks_done));
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+extern "C" int anemoi_sm100_push_out(const void* out_heads, void* const* peer_out,
+                                     void* const* peer_flags, const int64_t* first_rows,
+                                     int32_t self, int32_t ranks, int32_t heads_local,
+                                     int32_t head_dim, uint32_t epoch, void* blocks_done,
+                                     void* stream) {
+  if (!out_heads || !peer_out || !peer_flags || !first_rows || !blocks_done || ranks <= 0 ||
+      ranks > kMaxRanks || self < 0 || self >= ranks || heads_local <= 0 || head_dim <= 0 ||
+      head_dim % 8)
+    return ANEMOI_SM100_EINVAL;
+  PeerTable t{};
+  if (int rc = fill(t, peer_out, peer_flags, first_rows, ranks)) return rc;
+  const int d8 = head_dim / 8;
+  const int64_t total = first_rows[ranks] * heads_local * d8;
+  const int blocks = (int)max((int64_t)1, min((total + 255) / 256, (int64_t)(148 * 16)));
+  push_out_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(out_heads), t, self, ranks, heads_local, d8, total, epoch,
+      static_cast<unsigned int*>(blocks_done));
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+extern "C" int anemoi_sm100_wait_flags(const void* flags, int32_t ranks, uint32_t epoch,
+                                       uint64_t limit_ns, int32_t* status, void* stream) {
+  if (!flags || ranks <= 0 || ranks > kMaxRanks || limit_ns == 0 || limit_ns > 10000000000ull)
+    return ANEMOI_SM100_EINVAL;
+  wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(flags), ranks, epoch, limit_ns, status);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}

@@ -72,16 +72,19 @@ class H3BlockStack:
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
 
     def step(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, attention_fn, *, norm_rope,
-             group=None, pack=None, merge=None, on_attention=None) -> torch.Tensor:
+             group=None, pack=None, merge=None, on_attention=None, exchange=None) -> torch.Tensor:
         """One denoising step: every block in turn.  ``attention_fn(q, k, v)`` takes the
         head-sharded ``[S, h, D]`` tensors of a layer; ``norm_rope(x, weight, cos, sin, eps)`` is the
         producer fusion (in place, ``[1, rows, heads, D]``); ``on_attention(begin)`` is called with
-        True / False around the exchange + attention of each layer (timing hook)."""
+        True / False around the exchange + attention of each layer (timing hook); ``exchange`` is an
+        optional ``ulysses.PeerExchange`` (stores into the peers' memory instead of all-to-alls)."""
         c = self.config
         rows = x.size(0)
         kw = {}
         if pack is not None:
             kw.update(pack=pack, merge=merge)
+        if exchange is not None:
+            kw.update(exchange=exchange)
         for blk in self.blocks:
             shift1, scale1, gate1, shift2, scale2, gate2 = blk["mod"]
             h = self._norm(x, c.eps) * (1 + scale1) + shift1

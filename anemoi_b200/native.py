@@ -94,6 +94,15 @@ def library() -> C.CDLL:
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
         "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
         "anemoi_sm100_copy_rows": (C.c_int, [P, I64, P, I64, I64, I64, I32, P]),
+        "anemoi_sm100_peer_alloc": (C.c_int, [I64, C.POINTER(P), P]),
+        "anemoi_sm100_peer_open": (C.c_int, [P, C.POINTER(P)]),
+        "anemoi_sm100_peer_close": (C.c_int, [P]),
+        "anemoi_sm100_peer_free": (C.c_int, [P]),
+        "anemoi_sm100_push_qkv": (C.c_int, [P, P, P, C.POINTER(P), C.POINTER(P), C.POINTER(I64), I32, I32, I32,
+                                            I32, C.POINTER(I64), C.c_uint32, P, P]),
+        "anemoi_sm100_push_out": (C.c_int, [P, C.POINTER(P), C.POINTER(P), C.POINTER(I64), I32, I32, I32, I32,
+                                            C.c_uint32, P, P]),
+        "anemoi_sm100_wait_flags": (C.c_int, [P, I32, C.c_uint32, C.c_uint64, P, P]),
         "anemoi_sm100_set_wait_limit_ns": (C.c_int, [C.c_uint64]),
         "anemoi_sm100_wait_selftest": (C.c_int, [C.c_uint64, P, P]),
         "anemoi_sm100_assemble": (C.c_int, [SP, P, I64, C.c_int, P, P, P, P, P]),
@@ -123,7 +132,9 @@ EXPORTED = (
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
     "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
-    "anemoi_sm100_wait_selftest", "anemoi_sm100_copy_rows",
+    "anemoi_sm100_wait_selftest", "anemoi_sm100_copy_rows", "anemoi_sm100_push_qkv",
+    "anemoi_sm100_push_out", "anemoi_sm100_wait_flags", "anemoi_sm100_peer_alloc", "anemoi_sm100_peer_open",
+    "anemoi_sm100_peer_close", "anemoi_sm100_peer_free",
 )
 
 
@@ -387,6 +398,72 @@ def merge_heads(x: torch.Tensor, out: torch.Tensor | None = None, head_begin: in
                                                    head_begin, _stream(x.device)),
            "anemoi_sm100_merge_heads_into")
     return out
+
+
+def peer_alloc(nbytes: int) -> tuple[int, bytes]:
+    """A zero-filled device region of the current device and its 64-byte CUDA IPC handle."""
+    ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+    _check(library().anemoi_sm100_peer_alloc(nbytes, C.byref(ptr), handle), "anemoi_sm100_peer_alloc")
+    return int(ptr.value), handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    """Maps another process's region (same node) into this process; returns its address here."""
+    ptr = C.c_void_p()
+    _check(library().anemoi_sm100_peer_open(C.create_string_buffer(handle, 64), C.byref(ptr)),
+           "anemoi_sm100_peer_open")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    _check(library().anemoi_sm100_peer_close(C.c_void_p(ptr)), "anemoi_sm100_peer_close")
+
+
+def peer_free(ptr: int) -> None:
+    _check(library().anemoi_sm100_peer_free(C.c_void_p(ptr)), "anemoi_sm100_peer_free")
+
+
+def push_qkv(q, k, v, peer_recv, peer_flags, first_rows, rank: int, epoch: int, blocks_done) -> None:
+    """Store this rank's rows of ``q, k, v`` ``(rows, heads, D)`` into every rank's head-sharded
+    receive buffer ``(all rows, heads/world, 3*D)`` and publish ``epoch`` in their flag words;
+    ``peer_recv`` / ``peer_flags`` hold the addresses as mapped into this process."""
+    world = len(peer_recv)
+    rows, heads, d = q.shape
+    if rows != first_rows[rank + 1] - first_rows[rank]:
+        raise ValueError("q, k, v must hold exactly this rank's rows")
+    data = (C.c_void_p * world)(*peer_recv)
+    flags = (C.c_void_p * world)(*peer_flags)
+    first = (C.c_int64 * (world + 1))(*first_rows)
+    strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
+    _count("push_qkv", 1)
+    _check(library().anemoi_sm100_push_qkv(_ptr(q), _ptr(k), _ptr(v), data, flags, first, rank, world, heads, d,
+                                           strides, epoch & 0xFFFFFFFF, _ptr(blocks_done), _stream(q.device)),
+           "anemoi_sm100_push_qkv")
+
+
+def push_out(out_heads, peer_out, peer_flags, first_rows, rank: int, epoch: int, blocks_done) -> None:
+    """Store the head-sharded result ``(all rows, heads_local, D)`` into the sequence-sharded
+    output ``(its rows, world*heads_local, D)`` of the rank that owns each row and publish
+    ``epoch`` in the owners' flag words."""
+    world = len(peer_out)
+    total, heads_local, d = out_heads.shape
+    if not out_heads.is_contiguous() or total != first_rows[-1]:
+        raise ValueError("push_out needs the contiguous (all rows, heads_local, D) result")
+    data = (C.c_void_p * world)(*peer_out)
+    flags = (C.c_void_p * world)(*peer_flags)
+    first = (C.c_int64 * (world + 1))(*first_rows)
+    _count("push_out", 1)
+    _check(library().anemoi_sm100_push_out(_ptr(out_heads), data, flags, first, rank, world, heads_local, d,
+                                           epoch & 0xFFFFFFFF, _ptr(blocks_done), _stream(out_heads.device)),
+           "anemoi_sm100_push_out")
+
+
+def wait_flags(flags_ptr: int, world: int, epoch: int, limit_ns: int, status, device) -> None:
+    """One-warp kernel on the current stream: returns when every rank's flag has reached
+    ``epoch``; past ``limit_ns`` it records 70 + rank in ``status`` instead."""
+    _count("wait_flags", 1)
+    _check(library().anemoi_sm100_wait_flags(C.c_void_p(flags_ptr), world, epoch & 0xFFFFFFFF, limit_ns,
+                                             _ptr(status), _stream(device)), "anemoi_sm100_wait_flags")
 
 
 TENSOR_KINDS = {"f16": 0, "i8": 1, "f8": 2, "nvfp4": 3}

@@ -102,8 +102,154 @@ def head_groups(heads_local: int, groups: int) -> list[tuple[int, int]]:
     return out
 
 
+class _DeviceSpan:
+    """A raw device range offered to torch through the CUDA array interface (no copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+def first_rows(counts: list[int]) -> list[int]:
+    """First row of every rank's shard, with the total appended."""
+    out = [0]
+    for c in counts:
+        out.append(out[-1] + c)
+    return out
+
+
+def exchange_region_layout(counts: list[int], heads: int, head_dim: int, itemsize: int = 2) -> dict:
+    """Byte offsets inside a rank's exchange region; the same on every rank (the output slots are
+    sized for the longest shard): flag words, the head-sharded q|k|v receive buffer, two
+    sequence-sharded output slots used alternately."""
+    world = len(counts)
+    h_local = heads // world
+    align = lambda n: (n + 255) // 256 * 256          # noqa: E731
+    recv = sum(counts) * h_local * 3 * head_dim * itemsize
+    out = max(counts) * heads * head_dim * itemsize
+    layout = {"flags_in": 0, "flags_out": 64, "recv": 256}
+    layout["out0"] = layout["recv"] + align(recv)
+    layout["out1"] = layout["out0"] + align(out)
+    layout["bytes"] = layout["out1"] + align(out)
+    layout["recv_bytes"], layout["out_bytes"] = recv, out
+    return layout
+
+
+class PeerExchange:
+    """The Ulysses exchange by direct stores into the peers' memory, for the ranks of one node.
+
+    Construction is collective: every rank allocates one exchange region, the ranks swap its IPC
+    handle over the process group and map each other's regions.  Per layer, ``to_heads`` stores
+    this rank's rows of q, k, v into every rank's head-sharded receive buffer and returns the
+    local one once all ranks' parts have landed; ``to_sequence`` stores the head-sharded result
+    into the owners' output buffers and returns the local one likewise.  No collective library
+    call and no send, receive or merge copy is on the per-layer path: two store kernels and two
+    one-warp flag waits.  The calls must alternate (the hand-over that makes buffer reuse safe
+    depends on it); the returned output view is overwritten by the second ``to_sequence`` after
+    it.  A wait past ``limit_ns`` records 70 + the late rank in the device's sticky status word
+    (``executor.last_status``) and the stream continues."""
+
+    def __init__(self, rows_local: int, heads: int, head_dim: int, dtype, device, group=None,
+                 limit_ns: int = 10_000_000_000):
+        from .executor import _status_word
+
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("the exchange carries fp16 / bf16 rows")
+        self.group, self.device, self.dtype = group, torch.device(device), dtype
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if heads % self.world or self.world > 8:
+            raise ValueError(f"heads ({heads}) must divide the Ulysses degree ({self.world} <= 8)")
+        self.heads, self.head_dim, self.h_local = heads, head_dim, heads // self.world
+        self.counts = row_counts(rows_local, group)
+        self.first = first_rows(self.counts)
+        self.layout = exchange_region_layout(self.counts, heads, head_dim)
+        self.limit_ns = limit_ns
+        self.status = _status_word(self.device)
+        # set-up is collective and must not leave a rank behind: every rank reports how far it
+        # got, and all of them either finish or clean up and raise together
+        self.base, self.mapped, error = None, [], None
+        with torch.cuda.device(self.device):
+            try:
+                self.base, handle = native.peer_alloc(self.layout["bytes"])
+            except RuntimeError as exc:
+                handle, error = None, f"rank {self.rank}: {exc}"
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+            if error is None and all(h is not None for h in handles):
+                try:
+                    for r in range(self.world):
+                        self.mapped.append(self.base if r == self.rank else native.peer_open(handles[r]))
+                except RuntimeError as exc:
+                    error = f"rank {self.rank}: {exc}"
+            elif error is None:
+                error = f"rank {self.rank}: a peer could not allocate its region"
+            errors = [None] * self.world
+            dist.all_gather_object(errors, error, group=group)
+            if any(errors):
+                for r, ptr in enumerate(self.mapped):
+                    if r != self.rank:
+                        native.peer_close(ptr)
+                if self.base is not None:
+                    native.peer_free(self.base)
+                self.base = None
+                raise RuntimeError("peer exchange unavailable: " + "; ".join(e for e in errors if e))
+        at = lambda name: [b + self.layout[name] for b in self.mapped]      # noqa: E731
+        self.recv_ptrs, self.flags_in, self.flags_out = at("recv"), at("flags_in"), at("flags_out")
+        self.out_ptrs = (at("out0"), at("out1"))
+        self.region = torch.as_tensor(_DeviceSpan(self.base, self.layout["bytes"]), device=self.device)
+        lay, rows = self.layout, self.counts[self.rank]
+        self.recv = self.region[lay["recv"]:lay["recv"] + lay["recv_bytes"]].view(dtype).view(
+            self.first[-1], self.h_local, 3 * head_dim)
+        self.out = tuple(
+            self.region[lay[n]:lay[n] + rows * heads * head_dim * 2].view(dtype).view(rows, heads, head_dim)
+            for n in ("out0", "out1"))
+        self.blocks_done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.epoch, self.inbound = 0, False
+        dist.barrier(group=group)                # every region is mapped before anyone stores
+
+    def to_heads(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """``(rows_local, H, D)`` x3 -> ``(S, H/world, 3*D)``: this rank's heads of every row."""
+        if self.inbound:
+            raise RuntimeError("to_heads called twice without to_sequence in between")
+        self.epoch += 1
+        self.inbound = True
+        native.push_qkv(q, k, v, self.recv_ptrs, self.flags_in, self.first, self.rank, self.epoch,
+                        self.blocks_done)
+        native.wait_flags(self.flags_in[self.rank], self.world, self.epoch, self.limit_ns, self.status,
+                          self.device)
+        return self.recv
+
+    def to_sequence(self, out_heads: torch.Tensor) -> torch.Tensor:
+        """``(S, H/world, D)`` -> ``(rows_local, H, D)``."""
+        if not self.inbound:
+            raise RuntimeError("to_sequence called without a preceding to_heads")
+        self.inbound = False
+        slot = self.epoch & 1
+        native.push_out(out_heads, self.out_ptrs[slot], self.flags_out, self.first, self.rank, self.epoch,
+                        self.blocks_done)
+        native.wait_flags(self.flags_out[self.rank], self.world, self.epoch, self.limit_ns, self.status,
+                          self.device)
+        return self.out[slot]
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' regions and frees the own one."""
+        if self.base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)           # nobody stores into a region that is going away
+        self.recv = self.out = self.region = None
+        with torch.cuda.device(self.device):
+            for r, ptr in enumerate(self.mapped):
+                if r != self.rank:
+                    native.peer_close(ptr)
+            dist.barrier(group=self.group)
+            native.peer_free(self.base)
+        self.base = None
+
+
 def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_destination_major,
-                      merge=native.merge_heads, pipeline_groups: int = 1):
+                      merge=native.merge_heads, pipeline_groups: int = 1,
+                      exchange: PeerExchange | None = None):
     """Head-shard, run ``attention_fn(q, k, v)`` on ``[1, S, h, D]`` views, shard back.
 
     ``q, k, v``: ``[1, rows_local, H, D]`` (this rank's rows, every head).  Returns
@@ -116,10 +262,18 @@ def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_de
     attention kernels.  Every rank issues the same collectives in the same order.  The default is
     one group (one exchange each way): measured on 8 B200s two groups lose more to the split
     launches and to the collectives competing with the attention kernel for SMs (9.8 ms against
-    8.2 ms per layer) than the overlap wins; on 2 GPUs two groups are 0.5 % faster."""
+    8.2 ms per layer) than the overlap wins; on 2 GPUs two groups are 0.5 % faster.
+
+    With ``exchange`` (a ``PeerExchange`` built once for this shape and group) both all-to-alls
+    and their pack / merge copies are replaced by stores into the peers' memory."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return attention_fn(q, k, v)
+    if exchange is not None:
+        d = q.size(3)
+        recv = exchange.to_heads(q[0], k[0], v[0])
+        qh, kh, vh = (recv[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
+        return exchange.to_sequence(attention_fn(qh, kh, vh)[0].contiguous()).unsqueeze(0)
     rank = dist.get_rank(group)
     rows, heads, d = q.size(1), q.size(2), q.size(3)
     if heads % world:
@@ -163,13 +317,14 @@ def ulysses_anemoi_attention(q, k, v, *, layout: VisualLayout, layer: int,
                              sparse_config: SparseConfig | None = None,
                              quant_config: QuantConfig | None = None,
                              calibration: NVFP4Calibration | None = None, group=None,
-                             pipeline_groups: int = 1):
+                             pipeline_groups: int = 1, exchange: PeerExchange | None = None):
     """``anemoi_attention`` with the heads sharded over the ranks of ``group``."""
     def local(qh, kh, vh):
         return anemoi_attention(qh, kh, vh, layout=layout, layer=layer, sparse_config=sparse_config,
                                 quant_config=quant_config, calibration=calibration)
-    return ulysses_attention(q, k, v, local, group, pipeline_groups=pipeline_groups)
+    return ulysses_attention(q, k, v, local, group, pipeline_groups=pipeline_groups, exchange=exchange)
 
 
 __all__ = ["shard_rows", "row_counts", "reset_row_counts", "head_groups", "exchange_to_heads",
-           "exchange_to_sequence", "ulysses_attention", "ulysses_anemoi_attention"]
+           "exchange_to_sequence", "ulysses_attention", "ulysses_anemoi_attention", "PeerExchange",
+           "first_rows", "exchange_region_layout"]

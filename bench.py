@@ -441,13 +441,16 @@ def run_ours(args) -> None:
         dist.all_reduce(amax, op=dist.ReduceOp.MAX)
     calib = NVFP4Calibration(*[float(a) / (6 * 448) for a in amax.tolist()])
 
+    exchange, exchange_kind = open_exchange(args, world, rows[rank] if world > 1 else 0, w["heads"], w["dim"],
+                                            q.dtype, device)
+
     def layer(qq, kk, vv):
         if world == 1:
             return anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
                                     quant_config=quant, calibration=calib)
         return ulysses.ulysses_anemoi_attention(qq, kk, vv, layout=layout, layer=0, sparse_config=sparse,
                                                 quant_config=quant, calibration=calib,
-                                                pipeline_groups=args.pipeline_groups)
+                                                pipeline_groups=args.pipeline_groups, exchange=exchange)
 
     def barrier():
         if world > 1:
@@ -597,6 +600,7 @@ def run_ours(args) -> None:
                         "(QK of the 8-bit cell is kind::i8, its PV kind::f8f6f4)"}
         if world > 1:
             line["sharded_equals_single"] = sharded_ok
+            line["config"]["exchange"] = exchange_kind
         if world == 1 and not args.no_dense:
             line["dense_bf16"] = dense_flash_sample(q, k, v)
             line["error_vs_dense_fp32"] = error_versus_dense(q, k, v, out)
@@ -606,9 +610,30 @@ def run_ours(args) -> None:
                                     "cores": cpu["cores"], "kind": "port", "extrapolated": True,
                                     "sample": cpu["sample"]}
         print(json.dumps(line))
+    if exchange is not None:
+        exchange.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def open_exchange(args, world, rows_local, heads, dim, dtype, device):
+    """The transport of the Ulysses exchange at N > 1: stores into the peers' memory
+    (`--exchange peer`, and `auto` when the set-up succeeds on every rank) or NCCL
+    all_to_all_single (`--exchange nccl`, and `auto` otherwise); the JSON line names which."""
+    if world == 1:
+        return None, "none"
+    if args.exchange == "nccl":
+        return None, "nccl all_to_all_single + pack/merge kernels"
+    from anemoi_b200 import ulysses
+
+    try:
+        return (ulysses.PeerExchange(rows_local, heads, dim, dtype, device),
+                "stores into the peers' memory (CUDA IPC), flag hand-over, no collective call")
+    except RuntimeError as exc:
+        if args.exchange == "peer":
+            raise
+        return None, f"nccl all_to_all_single + pack/merge kernels ({exc})"
 
 
 # ------------------------------------------------------------------------------------------
@@ -686,9 +711,12 @@ def run_dit_step(args) -> None:
         e.record()
         marks.append(e)
 
+    exchange, exchange_kind = open_exchange(args, world, rows[rank], cfg.heads, cfg.head_dim, x.dtype, device)
+
     def one_step(timestep: float):
         attention.observe(timestep=torch.tensor(timestep), video_indices=None, position_ids=position_ids)
-        return stack.step(x, cos, sin, attention, norm_rope=fused_qknorm_rope, on_attention=on_attention)
+        return stack.step(x, cos, sin, attention, norm_rope=fused_qknorm_rope, on_attention=on_attention,
+                          exchange=exchange)
 
     def barrier():
         if world > 1:
@@ -732,9 +760,11 @@ def run_dit_step(args) -> None:
                                    f"SwiGLU {cfg.ffn_width} assumed, {cfg.rotary_dim} rotary channels assumed), "
                                    f"dense attention in the first {args.dit_dense_layers} layers, sparse "
                                    "NVFP4/INT8/FP16 40/40/20 at 80% drop elsewhere",
-                       "parallelism": f"ulysses{world}" if world > 1 else "single",
+                       "parallelism": f"ulysses{world}" if world > 1 else "single", "exchange": exchange_kind,
                        "dense_calls": stats["dense_calls"], "mpa_calls": stats["mpa_calls"]},
             "clocks": clocks.summary()}))
+    if exchange is not None:
+        exchange.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -834,6 +864,9 @@ def main() -> None:
                     help="skip the dense bf16 library attention timed beside the sparse layer")
     ap.add_argument("--e2e-group-heads", type=int, default=8,
                     help="heads per group of the pipelined host-input call (end-to-end number)")
+    ap.add_argument("--exchange", choices=("auto", "peer", "nccl"), default="auto",
+                    help="N > 1: Ulysses exchange by stores into the peers' memory, by NCCL all-to-all, or "
+                         "the first if its set-up succeeds on every rank")
     ap.add_argument("--pipeline-groups", type=int, default=1,
                     help="head groups whose exchange is pipelined under the attention (N > 1)")
     ap.add_argument("--config", choices=("layer", "dit-step"), default="layer",

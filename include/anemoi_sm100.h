@@ -224,6 +224,45 @@ int anemoi_sm100_merge_heads_into(const void* recv, void* out, int64_t rows, int
                                   int32_t head_count, int32_t head_dim, int32_t heads_per_rank,
                                   int32_t head_begin, void* stream);
 
+/* The Ulysses exchange by direct stores into the peers' memory (one node, at most 8 ranks), in
+ * place of pack + all-to-all and all-to-all + merge: fused with the collective between them,
+ * they replace pack_qkv_destination_major + all_to_all_single and all_to_all_single +
+ * merge_heads of the reference (optimized/ulysses_custom.py:107-165, relayout.py:83-162).
+ *
+ * Set-up (not on the hot path): every rank allocates one exchange region with peer_alloc
+ * (cudaMalloc, zero-filled, exported as a 64-byte CUDA IPC handle), passes the handle to the other
+ * processes of the node by any host channel, and maps theirs with peer_open; peer_close unmaps,
+ * peer_free releases the own region.
+ *
+ * Per layer: `peer_*[r]` is rank r's buffer / flag words as mapped into this process (`[self]`
+ * the local ones); `first_rows[ranks+1]` the first row of every rank's sequence shard.
+ *   push_qkv : this rank's rows of q,k,v [rows][heads][D] (strides as in pack_qkv)
+ *              -> on rank r: recv [all rows][heads/ranks][3*D], rows first_rows[self]..
+ *   push_out : out_heads [all rows][heads_local][D] (this rank's heads, every row)
+ *              -> on the owner of a row: out [its rows][ranks*heads_local][D]
+ * Plain 16-byte stores over NVLink.  The last block of a push writes `epoch` into word [self] of
+ * every destination's flags (release, system scope); `blocks_done` is a zeroed device word of
+ * the caller, private to the stream.  wait_flags (one warp, next in stream order on the
+ * destination) returns when the first `ranks` words of `flags` have all reached `epoch`, or
+ * after `limit_ns` (at most 10 s) with 70 + the late rank in the sticky status word.  Epochs
+ * grow by one per call and compare modulo 2^32.  Ordering that makes buffer reuse safe: a rank
+ * pushes q,k,v of call e only after its wait on the outputs of call e-1, and pushes outputs
+ * of call e only after its wait on the inputs of call e. */
+int anemoi_sm100_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int anemoi_sm100_peer_open(const void* handle64, void** ptr);
+int anemoi_sm100_peer_close(void* ptr);
+int anemoi_sm100_peer_free(void* ptr);
+int anemoi_sm100_push_qkv(const void* q, const void* k, const void* v, void* const* peer_recv,
+                          void* const* peer_flags, const int64_t* first_rows, int32_t self,
+                          int32_t ranks, int32_t heads, int32_t head_dim, const int64_t* strides,
+                          uint32_t epoch, void* blocks_done, void* stream);
+int anemoi_sm100_push_out(const void* out_heads, void* const* peer_out, void* const* peer_flags,
+                          const int64_t* first_rows, int32_t self, int32_t ranks,
+                          int32_t heads_local, int32_t head_dim, uint32_t epoch, void* blocks_done,
+                          void* stream);
+int anemoi_sm100_wait_flags(const void* flags, int32_t ranks, uint32_t epoch, uint64_t limit_ns,
+                            int32_t* status, void* stream);
+
 /* One strided copy between pinned host memory and the device (rows of `width` bytes, `height`
  * of them, pitches in bytes): a group of heads of a host [1,S,H,D] tensor to or from a
  * contiguous device [1,S,heads,D] tensor.  Used by the host-input entry of the Python layer to

@@ -1,4 +1,5 @@
-"""GPU (2 or more devices): the head-sharded Ulysses run equals the single-GPU run bit for bit."""
+"""GPU (2 or more devices): the head-sharded Ulysses run equals the single-GPU run bit for bit,
+through the all-to-all exchange and through the stores into the peers' memory."""
 
 import os
 import socket
@@ -30,7 +31,20 @@ def _worker(rank, world, port, results):
         mine = [t[:, lo : lo + rows[rank]].contiguous().cuda() for t in (q, k, v)]
         got = ulysses.ulysses_anemoi_attention(*mine, **kw)
         torch.cuda.synchronize()
-        results[rank] = bool(torch.equal(got, full[:, lo : lo + rows[rank]]))
+        ok = bool(torch.equal(got, full[:, lo : lo + rows[rank]]))
+        # the same through stores into the peers' memory, three layers in a row (buffer reuse)
+        from anemoi_b200.executor import last_status
+
+        peer = ulysses.PeerExchange(rows[rank], heads, 128, torch.bfloat16, torch.device("cuda", rank))
+        try:
+            for _ in range(3):
+                got = ulysses.ulysses_anemoi_attention(*mine, exchange=peer, **kw)
+                torch.cuda.synchronize()
+                ok = ok and bool(torch.equal(got, full[:, lo : lo + rows[rank]]))
+            ok = ok and last_status(torch.device("cuda", rank)) == 0
+        finally:
+            peer.close()
+        results[rank] = ok
     finally:
         dist.destroy_process_group()
 

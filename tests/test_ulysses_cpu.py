@@ -148,3 +148,12 @@ def test_block_stack_sharded_equals_unsharded():
     results = mp.Manager().dict()
     mp.spawn(_stack_worker, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+def test_exchange_region_layout_is_aligned_and_disjoint():
+    from anemoi_b200.ulysses import exchange_region_layout
+
+    lay = exchange_region_layout([301, 300, 300], 6, 128)
+    assert lay["recv"] % 256 == 0 and lay["out0"] % 256 == 0 and lay["out1"] % 256 == 0
+    assert lay["recv"] + lay["recv_bytes"] <= lay["out0"]
+    assert lay["out0"] + lay["out_bytes"] <= lay["out1"] <= lay["bytes"] - lay["out_bytes"]
