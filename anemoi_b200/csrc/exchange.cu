@@ -123,9 +123,12 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int ranks, uint32_t epo
   if (status) atomicCAS(status, 0, 70 + r);
 }
 
-int fill(PeerTable& t, void* const* data, void* const* flags, const int64_t* first, int ranks) {
+// `own_rows`: the buffers hold only their rank's rows, so a rank without rows may have none
+int fill(PeerTable& t, void* const* data, void* const* flags, const int64_t* first, int ranks,
+         bool own_rows) {
   for (int r = 0; r < ranks; ++r) {
-    if (!data[r] || !flags[r] || first[r + 1] < first[r]) return ANEMOI_SM100_EINVAL;
+    if (!flags[r] || first[r + 1] < first[r]) return ANEMOI_SM100_EINVAL;
+    if (!data[r] && !(own_rows && first[r + 1] == first[r])) return ANEMOI_SM100_EINVAL;
     t.data[r] = static_cast<uint16_t*>(data[r]);
     t.flags[r] = static_cast<uint32_t*>(flags[r]);
     t.first[r] = first[r];
@@ -184,7 +187,7 @@ extern "C" int anemoi_sm100_push_qkv(const void* q, const void* k, const void* v
   for (int i = 0; i < 6; ++i)
     if (strides[i] % 8) return ANEMOI_SM100_EINVAL;
   PeerTable t{};
-  if (int rc = fill(t, peer_recv, peer_flags, first_rows, ranks)) return rc;
+  if (int rc = fill(t, peer_recv, peer_flags, first_rows, ranks, false)) return rc;
   const int64_t rows = first_rows[self + 1] - first_rows[self];
   if (rows > 0 && (!q || !k || !v)) return ANEMOI_SM100_EINVAL;   // a rank without rows has no tensors
   const int heads_local = heads / ranks, d8 = head_dim / 8;
@@ -209,7 +212,7 @@ extern "C" int anemoi_sm100_push_out(const void* out_heads, void* const* peer_ou
       head_dim % 8)
     return ANEMOI_SM100_EINVAL;
   PeerTable t{};
-  if (int rc = fill(t, peer_out, peer_flags, first_rows, ranks)) return rc;
+  if (int rc = fill(t, peer_out, peer_flags, first_rows, ranks, true)) return rc;
   const int d8 = head_dim / 8;
   const int64_t total = first_rows[ranks] * heads_local * d8;
   const int blocks = (int)max((int64_t)1, min((total + 255) / 256, (int64_t)(148 * 16)));
