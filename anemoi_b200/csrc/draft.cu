@@ -22,10 +22,9 @@
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kRowsPerWarp = 2;
-constexpr int kRows = kWarps * kRowsPerWarp;  // query blocks per CTA
 constexpr int kChunk = 128;                   // key blocks per pass: 4 per lane
 constexpr int kPitch = kChunk + 4;            // floats per channel row of the key tile
+constexpr int kSlab = 64;                     // channels of the key tile held at a time
 constexpr int kMaxBlocks = 4096;              // rows per head the shared-memory buffers allow
 
 __device__ __forceinline__ float exp_canonical(float t) {
@@ -43,58 +42,78 @@ __device__ __forceinline__ float exp_canonical(float t) {
   return __fmul_rn(p, __int_as_float((static_cast<int>(n) + 127) << 23));
 }
 
-// fp16 logits of kRows query blocks against every key block of the head.  Each warp owns
-// two rows, each lane four key columns of the 128-column pass: per channel one 16-byte
-// load of keys and one 8-byte load of the two query values feed eight FMAs.  Every logit
-// is still the plain channel-ordered FMA chain (the canonical order).
-template <int D>
+// fp16 logits of kWarps * RPW query blocks against every key block of the head.  Each warp owns
+// RPW (2 or 4) rows, each lane four key columns of the 128-column pass: per channel one 16-byte
+// load of keys (four shared-memory wavefronts per warp) and one broadcast load of the warp's
+// query values feed 4 * RPW FMAs, so with four rows the FMA pipe rather than shared memory
+// sets the pace.  Every logit is still the plain channel-ordered FMA chain (the canonical
+// order).
+template <int D, int RPW>
 __device__ __forceinline__ void row_logits(const __half* q_pool, const __half* k_pool, int head,
                                            int R, int row0, float* kc, float* qs, __half* lg,
                                            int lg_stride) {
+  constexpr int kRows = kWarps * RPW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float scale = D == 64 ? 0.125f : __int_as_float(0x3db504f3);
-  // query pools as floats, the two rows of a warp interleaved: qs[warp][channel][2]
+  // query pools as floats, the rows of a warp interleaved: qs[warp][channel][RPW]
   for (int idx = threadIdx.x; idx < kRows * D; idx += kWarps * 32) {
     const int r = idx / D, c = idx % D;
     const int row = row0 + r;
-    qs[((r >> 1) * D + c) * 2 + (r & 1)] =
+    qs[((r / RPW) * D + c) * RPW + (r % RPW)] =
         row < R ? __half2float(q_pool[((int64_t)head * R + row) * D + c]) : 0.0f;
   }
   for (int c0 = 0; c0 < R; c0 += kChunk) {
-    __syncthreads();
-    // key pools of columns [c0, c0 + kChunk) transposed to [channel][column] floats
-    for (int idx = threadIdx.x; idx < kChunk * (D / 8); idx += kWarps * 32) {
-      const int col = idx % kChunk, c8 = idx / kChunk;
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (c0 + col < R)
-        raw = __ldg(reinterpret_cast<const uint4*>(k_pool + ((int64_t)head * R + c0 + col) * D) + c8);
-      const __half* h = reinterpret_cast<const __half*>(&raw);
+    float acc[RPW][4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) kc[(c8 * 8 + i) * kPitch + col] = __half2float(h[i]);
-    }
-    __syncthreads();
-    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const float* qw = qs + warp * D * 2;
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+    const float* qw = qs + warp * D * RPW;
+    // the key tile is staged kSlab channels at a time; the chain still runs over c = 0..D-1
+    for (int s0 = 0; s0 < D; s0 += kSlab) {
+      __syncthreads();
+      // key pools of columns [c0, c0 + kChunk), channels [s0, s0 + kSlab), as [channel][column] floats
+      for (int idx = threadIdx.x; idx < kChunk * (kSlab / 8); idx += kWarps * 32) {
+        const int col = idx % kChunk, c8 = idx / kChunk;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (c0 + col < R)
+          raw = __ldg(reinterpret_cast<const uint4*>(k_pool + ((int64_t)head * R + c0 + col) * D + s0) + c8);
+        const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kc[(c8 * 8 + i) * kPitch + col] = __half2float(h[i]);
+      }
+      __syncthreads();
 #pragma unroll 4
-    for (int c = 0; c < D; ++c) {
-      const float2 qv = *reinterpret_cast<const float2*>(qw + c * 2);
-      const float4 kv = *reinterpret_cast<const float4*>(kc + c * kPitch + lane * 4);
-      acc[0][0] = __fmaf_rn(qv.x, kv.x, acc[0][0]);
-      acc[0][1] = __fmaf_rn(qv.x, kv.y, acc[0][1]);
-      acc[0][2] = __fmaf_rn(qv.x, kv.z, acc[0][2]);
-      acc[0][3] = __fmaf_rn(qv.x, kv.w, acc[0][3]);
-      acc[1][0] = __fmaf_rn(qv.y, kv.x, acc[1][0]);
-      acc[1][1] = __fmaf_rn(qv.y, kv.y, acc[1][1]);
-      acc[1][2] = __fmaf_rn(qv.y, kv.z, acc[1][2]);
-      acc[1][3] = __fmaf_rn(qv.y, kv.w, acc[1][3]);
+      for (int c = 0; c < kSlab; ++c) {
+        float qv[RPW];
+        if (RPW == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(qw + (s0 + c) * 4);
+          qv[0] = t.x;
+          qv[1] = t.y;
+          qv[RPW - 2] = t.z;
+          qv[RPW - 1] = t.w;
+        } else {
+          const float2 t = *reinterpret_cast<const float2*>(qw + (s0 + c) * 2);
+          qv[0] = t.x;
+          qv[1] = t.y;
+        }
+        const float4 kv = *reinterpret_cast<const float4*>(kc + c * kPitch + lane * 4);
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          acc[r][0] = __fmaf_rn(qv[r], kv.x, acc[r][0]);
+          acc[r][1] = __fmaf_rn(qv[r], kv.y, acc[r][1]);
+          acc[r][2] = __fmaf_rn(qv[r], kv.z, acc[r][2]);
+          acc[r][3] = __fmaf_rn(qv[r], kv.w, acc[r][3]);
+        }
+      }
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int r = 0; r < RPW; ++r)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int col = c0 + lane * 4 + j;
         if (col < R)
-          lg[(warp * 2 + r) * lg_stride + col] = __float2half_rn(__fmul_rn(acc[r][j], scale));
+          lg[(warp * RPW + r) * lg_stride + col] = __float2half_rn(__fmul_rn(acc[r][j], scale));
       }
   }
   __syncwarp();
@@ -115,29 +134,30 @@ __device__ __forceinline__ void row_stats(const __half* lg, int R, float& mx, fl
   inv = __fdiv_rn(1.0f, s);
 }
 
-template <int D, bool kBlend>
+template <int D, bool kBlend, int RPW>
 __global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool,
                                                             const __half* k_pool,
                                                             const __half* q_max, const __half* k_max,
                                                             float w, int R, __half* prob) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr int kRows = kWarps * RPW;
   const int lg_stride = (R + 7) & ~7;
-  float* kc = reinterpret_cast<float*>(smem_raw);                   // [D][kPitch]
-  float* qs = kc + D * kPitch;                                      // [kWarps][D][2]
+  float* kc = reinterpret_cast<float*>(smem_raw);                   // [kSlab][kPitch]
+  float* qs = kc + kSlab * kPitch;                                      // [kWarps][D][2]
   __half* lg = reinterpret_cast<__half*>(qs + kRows * D);           // [kRows][lg_stride]
   __half* lgx = lg + kRows * lg_stride;                             // blend only
   const int head = blockIdx.y, row0 = blockIdx.x * kRows;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  row_logits<D>(q_pool, k_pool, head, R, row0, kc, qs, lg, lg_stride);
+  row_logits<D, RPW>(q_pool, k_pool, head, R, row0, kc, qs, lg, lg_stride);
   if (kBlend) {
     __syncthreads();
-    row_logits<D>(q_max, k_max, head, R, row0, kc, qs, lgx, lg_stride);
+    row_logits<D, RPW>(q_max, k_max, head, R, row0, kc, qs, lgx, lg_stride);
   }
-  for (int r = 0; r < kRowsPerWarp; ++r) {
-    const int row = row0 + warp * 2 + r;
+  for (int r = 0; r < RPW; ++r) {
+    const int row = row0 + warp * RPW + r;
     if (row >= R) break;
-    const __half* mine = lg + (warp * 2 + r) * lg_stride;
+    const __half* mine = lg + (warp * RPW + r) * lg_stride;
     float m, inv;
     row_stats(mine, R, m, inv);
     __half* out = prob + ((int64_t)head * R + row) * R;
@@ -145,7 +165,7 @@ __global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool
       for (int j = lane; j < R; j += 32)
         out[j] = __float2half_rn(__fmul_rn(exp_canonical(__fsub_rn(__half2float(mine[j]), m)), inv));
     } else {
-      const __half* minex = lgx + (warp * 2 + r) * lg_stride;
+      const __half* minex = lgx + (warp * RPW + r) * lg_stride;
       float mxx, invx;
       row_stats(minex, R, mxx, invx);
       const float wm = __fsub_rn(1.0f, w);
@@ -158,19 +178,34 @@ __global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool
   }
 }
 
-template <int D, bool kBlend>
-int launch(const __half* qp, const __half* kp, const __half* qx, const __half* kx, float w, int R,
-           int H, __half* prob, cudaStream_t st) {
-  const int lg_stride = (R + 7) & ~7;
-  const size_t smem = (size_t)D * kPitch * 4 + (size_t)kRows * D * 4 +
-                      (size_t)kRows * lg_stride * 2 * (kBlend ? 2 : 1);
-  auto kernel = draft_kernel<D, kBlend>;
+// Shared memory of one CTA: key tile, query rows, the logits of its rows (twice when blending).
+template <int D, bool kBlend, int RPW>
+constexpr size_t smem_bytes(int R) {
+  return (size_t)kSlab * kPitch * 4 + (size_t)kWarps * RPW * D * 4 +
+         (size_t)kWarps * RPW * ((R + 7) & ~7) * 2 * (kBlend ? 2 : 1);
+}
+
+template <int D, bool kBlend, int RPW>
+int launch_rows(const __half* qp, const __half* kp, const __half* qx, const __half* kx, float w, int R,
+                int H, __half* prob, cudaStream_t st) {
+  const size_t smem = smem_bytes<D, kBlend, RPW>(R);
+  auto kernel = draft_kernel<D, kBlend, RPW>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
+  constexpr int kRows = kWarps * RPW;
   dim3 grid((R + kRows - 1) / kRows, H);
   kernel<<<grid, kWarps * 32, smem, st>>>(qp, kp, qx, kx, w, R, prob);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+// Four rows per warp while two CTAs still fit an SM's shared memory, else two rows per warp.
+template <int D, bool kBlend>
+int launch(const __half* qp, const __half* kp, const __half* qx, const __half* kx, float w, int R,
+           int H, __half* prob, cudaStream_t st) {
+  if (smem_bytes<D, kBlend, 4>(R) <= 113 * 1024)
+    return launch_rows<D, kBlend, 4>(qp, kp, qx, kx, w, R, H, prob, st);
+  return launch_rows<D, kBlend, 2>(qp, kp, qx, kx, w, R, H, prob, st);
 }
 
 }  // namespace

@@ -13,9 +13,13 @@
 //
 // Here the sort is replaced by selection.  A 32768-bin histogram of the keys of
 // a head gives, for each of the three rank boundaries, the key that straddles it
-// and how many items of that key fall above it; only items whose key equals a
-// straddling key need their position inside the bin, which is their count in
-// earlier rows (a per-row tally) plus their count earlier in the same row.
+// and how many items of that key fall above it (the quota).  One pass per row then
+// counts the keys above and equal to each straddling key; a per-head scan over the
+// rows turns the equal-counts into each row's position inside the straddling bins,
+// from which the row's stages per phase, its list offset (an exclusive scan: the
+// layout is the same at every call) and the launch order follow without touching
+// the map again; a last pass per row writes the lists.  The per-row passes use one
+// warp per row: ranks inside a row come from ballots, no block-wide barrier.
 #include <cuda_fp16.h>
 
 #include "records.cuh"
@@ -24,17 +28,17 @@ namespace {
 
 constexpr int kBins = 32768;
 constexpr int kHistThreads = 512;
-constexpr int kRowThreads = 256;
+constexpr int kRowWarps = 8;  // rows per CTA in the per-row passes, one warp each
+constexpr int kStat = 6;      // ints per row: keys above boundary 0,1,2; keys equal to its key 0,1,2
 
 struct RouteScratch {
-  int* hist;    // [H][kBins]
-  int* thr;     // [H][8]: key0, quota0, key1, quota1, key2, quota2, -, -
-  int* eq;      // [H][R][4]: items per row equal to straddling key 0,1,2
-  int* cursor;  // [H]
+  int* hist;  // [H][kBins]
+  int* thr;   // [H][8]: key0, quota0, key1, quota1, key2, quota2, -, -
+  int* stat;  // [H][R][kStat]; the equal-counts become exclusive prefixes over the rows
 };
 
 __host__ __device__ inline int64_t scratch_ints(int H, int R) {
-  return (int64_t)H * (kBins + 8 + 4 * (int64_t)R + 1);
+  return (int64_t)H * (kBins + 8 + kStat * (int64_t)R);
 }
 
 __global__ void __launch_bounds__(kHistThreads) hist_kernel(const unsigned short* prob,
@@ -55,222 +59,246 @@ __global__ void __launch_bounds__(kHistThreads) hist_kernel(const unsigned short
     if (local[i]) atomicAdd(out + i, local[i]);
 }
 
-// One CTA per head: walks the histogram from the largest key down and records,
-// for each boundary B, the key whose bin contains rank B and B's offset in it.
-__global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* thr, int64_t b0,
-                                                         int64_t b1, int64_t b2) {
-  __shared__ int64_t warp_sum[32];
-  __shared__ int result[8];
-  const int head = blockIdx.x;
-  const int* h = hist + (int64_t)head * kBins;
-  // thread t owns keys [hi_key - 31, hi_key], hi_key = kBins - 1 - 32 t
-  const int hi_key = kBins - 1 - 32 * threadIdx.x;
-  int mine[32];
-  int64_t total = 0;
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    mine[i] = h[hi_key - i];
-    total += mine[i];
-  }
-  // exclusive prefix over threads (descending keys)
-  int64_t incl = total;
+// Exclusive prefix of `v` over the threads of a 1024-thread CTA; `total` gets the sum.
+// `warp_sum` is shared scratch of 32 entries; the call ends with the scratch free again.
+__device__ __forceinline__ long long block_exclusive(long long v, long long* warp_sum,
+                                                     long long& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  long long incl = v;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    int64_t n = __shfl_up_sync(0xffffffffu, incl, off);
+    const long long n = __shfl_up_sync(0xffffffffu, incl, off);
     if (lane >= off) incl += n;
   }
   if (lane == 31) warp_sum[warp] = incl;
-  if (threadIdx.x < 8) result[threadIdx.x] = threadIdx.x & 1 ? 0 : -1;
   __syncthreads();
-  int64_t base = 0;
-  for (int w = 0; w < warp; ++w) base += warp_sum[w];
-  int64_t above = base + incl - total;
-  const int64_t bound[3] = {b0, b1, b2};
+  long long base = 0, all = 0;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const int64_t next = above + mine[i];
-#pragma unroll
-    for (int b = 0; b < 3; ++b) {
-      if (mine[i] > 0 && above <= bound[b] && bound[b] < next) {
-        result[2 * b] = hi_key - i;
-        result[2 * b + 1] = (int)(bound[b] - above);
-      }
-    }
-    above = next;
+  for (int w = 0; w < 32; ++w) {
+    const long long t = warp_sum[w];
+    base += w < warp ? t : 0;
+    all += t;
   }
   __syncthreads();
-  if (threadIdx.x < 8) thr[head * 8 + threadIdx.x] = result[threadIdx.x];
+  total = all;
+  return base + incl - v;
 }
 
-__global__ void __launch_bounds__(kRowThreads) tally_kernel(const unsigned short* prob, int R,
-                                                            const int* thr, int* eq) {
-  __shared__ int acc[3];
-  const int row = blockIdx.x, head = blockIdx.y;
-  if (threadIdx.x < 3) acc[threadIdx.x] = 0;
+// One CTA per head: finds, for each boundary B, the key whose bin contains rank B (keys
+// ranked from the largest down) and B's offset inside that bin.  Two levels: sums of 32-bin
+// blocks (coalesced reads, one warp reduction each), a scan over the 1024 blocks, then one
+// warp per boundary resolves the bin inside the block that straddles it.
+__global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* thr, int64_t b0,
+                                                         int64_t b1, int64_t b2) {
+  __shared__ long long warp_sum[32];
+  __shared__ int block_sum[1024];
+  __shared__ int hit_block[3];
+  __shared__ long long hit_off[3];
+  const int head = blockIdx.x;
+  const int* h = hist + (int64_t)head * kBins;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int mine = 0;
+#pragma unroll 4
+  for (int i = 0; i < 32; ++i) {
+    const int sum = __reduce_add_sync(0xffffffffu, h[(warp * 32 + i) * 32 + lane]);
+    if (lane == i) mine = sum;
+  }
+  block_sum[threadIdx.x] = mine;
+  if (threadIdx.x < 3) hit_block[threadIdx.x] = -1;
   __syncthreads();
+  // thread t owns block 1023 - t: blocks in descending key order
+  const int blk = 1023 - threadIdx.x;
+  const long long total = block_sum[blk];
+  long long all;
+  const long long above = block_exclusive(total, warp_sum, all);
+  const long long bound[3] = {b0, b1, b2};
+#pragma unroll
+  for (int b = 0; b < 3; ++b)
+    if (total > 0 && above <= bound[b] && bound[b] < above + total) {
+      hit_block[b] = blk;
+      hit_off[b] = bound[b] - above;
+    }
+  __syncthreads();
+  if (warp < 3) {
+    int key = -1, quota = 0;  // boundary at or past the last item: every key lies above it
+    const int hb = hit_block[warp];
+    if (hb >= 0) {
+      const int bin = hb * 32 + 31 - lane;  // descending inside the block
+      const int n = h[bin];
+      int incl = n;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int m = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += m;
+      }
+      const long long off = hit_off[warp];
+      const bool here = n > 0 && incl - n <= off && off < incl;
+      const unsigned who = __ballot_sync(0xffffffffu, here);
+      const int src = __ffs(who) - 1;
+      key = __shfl_sync(0xffffffffu, bin, src);
+      quota = __shfl_sync(0xffffffffu, (int)(off - (incl - n)), src);
+    }
+    if (lane == 0) {
+      thr[head * 8 + 2 * warp] = key;
+      thr[head * 8 + 2 * warp + 1] = quota;
+    }
+  }
+}
+
+// One warp per row: keys above each straddling key, keys equal to it.
+__global__ void __launch_bounds__(kRowWarps * 32) rowstat_kernel(const unsigned short* prob, int R,
+                                                                 const int* thr, int* stat) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (row >= R) return;
+  const int lane = threadIdx.x & 31;
   const int k0 = thr[head * 8], k1 = thr[head * 8 + 2], k2 = thr[head * 8 + 4];
   const unsigned short* src = prob + ((int64_t)head * R + row) * R;
-  int c0 = 0, c1 = 0, c2 = 0;
-  for (int j = threadIdx.x; j < R; j += kRowThreads) {
+  int g0 = 0, g1 = 0, g2 = 0, e0 = 0, e1 = 0, e2 = 0;
+  for (int j = lane; j < R; j += 32) {
     const int key = __ldg(src + j) & 0x7fff;
-    c0 += key == k0;
-    c1 += key == k1;
-    c2 += key == k2;
+    g0 += key > k0;
+    g1 += key > k1;
+    g2 += key > k2;
+    e0 += key == k0;
+    e1 += key == k1;
+    e2 += key == k2;
   }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    c0 += __shfl_xor_sync(0xffffffffu, c0, off);
-    c1 += __shfl_xor_sync(0xffffffffu, c1, off);
-    c2 += __shfl_xor_sync(0xffffffffu, c2, off);
+  g0 = __reduce_add_sync(0xffffffffu, g0);
+  g1 = __reduce_add_sync(0xffffffffu, g1);
+  g2 = __reduce_add_sync(0xffffffffu, g2);
+  e0 = __reduce_add_sync(0xffffffffu, e0);
+  e1 = __reduce_add_sync(0xffffffffu, e1);
+  e2 = __reduce_add_sync(0xffffffffu, e2);
+  if (lane < kStat) {
+    const int v = lane == 0 ? g0 : lane == 1 ? g1 : lane == 2 ? g2 : lane == 3 ? e0 : lane == 4 ? e1 : e2;
+    stat[((int64_t)head * R + row) * kStat + lane] = v;
   }
-  if ((threadIdx.x & 31) == 0) {
-    atomicAdd(&acc[0], c0);
-    atomicAdd(&acc[1], c1);
-    atomicAdd(&acc[2], c2);
-  }
-  __syncthreads();
-  if (threadIdx.x < 3) eq[((int64_t)head * R + row) * 4 + threadIdx.x] = acc[threadIdx.x];
 }
 
-// Ordered rank of a flagged thread inside the CTA: flagged threads of lower
-// thread index in this call + `running`; `running` is advanced by the total.
-__device__ __forceinline__ int ordered_rank(bool flag, int& running, int* warp_tot) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-  __syncthreads();
-  if (lane == 0) warp_tot[warp] = __popc(ballot);
-  __syncthreads();
-  int before = 0, total = 0;
+// One CTA per head, rows in chunks of 1024: position of every row inside the straddling bins
+// (exclusive scan of the equal-counts), hence its stages per phase, and its list offset
+// (exclusive scan of the totals).  Then the launch order of the head's query blocks for the
+// attention kernel: longest list first (ties by block index), written as block + 1 into the
+// fourth entry of row_counts, slot = position; the last CTAs of a launch are then the short
+// ones, which shortens the tail during which SMs run out of work.  Blocks are ranked by
+// counting (R^2 / threads comparisons per thread); very large block counts keep the identity
+// order (the fourth entries stay 0).
+constexpr int kOrderMaxBlocks = 4096;
+__global__ void __launch_bounds__(1024) headscan_kernel(int R, const int* thr, int* stat, int factor,
+                                                        int prefix_stages, int prefix_phase,
+                                                        int32_t* row_offset, int32_t* row_counts) {
+  __shared__ long long warp_sum[32];
+  __shared__ int total_s[kOrderMaxBlocks];
+  const int head = blockIdx.x;
+  int quota[3];
 #pragma unroll
-  for (int w = 0; w < kRowThreads / 32; ++w) {
-    const int t = warp_tot[w];
-    before += w < warp ? t : 0;
-    total += t;
+  for (int b = 0; b < 3; ++b) quota[b] = thr[head * 8 + 2 * b + 1];
+  const int p = prefix_phase >= 0 ? prefix_stages : 0;
+  long long carry[4] = {0, 0, 0, 0};  // equal-counts of earlier rows (3), stages of earlier rows
+  for (int r0 = 0; r0 < R; r0 += 1024) {
+    const int row = r0 + threadIdx.x;
+    const bool in = row < R;
+    int* st = stat + ((int64_t)head * R + row) * kStat;
+    int below[3];
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      const int eq = in ? st[3 + b] : 0;
+      long long all;
+      const long long pre = carry[b] + block_exclusive(eq, warp_sum, all);
+      carry[b] += all;
+      // items of the straddling key in this row that still fall above the boundary
+      const long long room = (long long)quota[b] - pre;
+      const int take = (int)max(0ll, min((long long)eq, room));
+      below[b] = in ? st[b] + take : 0;
+      if (in) st[3 + b] = (int)pre;
+    }
+    int n[3];
+    n[0] = (below[2] - below[1]) * factor + (prefix_phase == 0 ? p : 0);  // NVFP4
+    n[1] = (below[1] - below[0]) * factor + (prefix_phase == 1 ? p : 0);  // INT8
+    n[2] = below[0] * factor + (prefix_phase == 2 ? p : 0);               // FP16
+    const int total = in ? n[0] + n[1] + n[2] : 0;
+    long long all;
+    const long long off = carry[3] + block_exclusive(total, warp_sum, all);
+    carry[3] += all;
+    if (in) {
+      row_offset[(int64_t)head * R + row] = (int32_t)off;
+      int32_t* rc = row_counts + ((int64_t)head * R + row) * 4;
+      rc[0] = n[0];
+      rc[1] = n[1];
+      rc[2] = n[2];
+      rc[3] = 0;
+      if (row < kOrderMaxBlocks) total_s[row] = total;
+    }
   }
-  const int rank = running + before + __popc(ballot & ((1u << lane) - 1u));
-  running += total;
-  return rank;
+  if (R > kOrderMaxBlocks) return;
+  __syncthreads();
+  int32_t* rc = row_counts + (int64_t)head * R * 4;
+  for (int i = threadIdx.x; i < R; i += 1024) {
+    const int mine = total_s[i];
+    int rank = 0;
+    for (int j = 0; j < R; ++j) rank += (total_s[j] > mine) || (total_s[j] == mine && j < i);
+    rc[rank * 4 + 3] = i + 1;
+  }
 }
 
-__global__ void __launch_bounds__(kRowThreads) emit_kernel(
-    const unsigned short* prob, int R, const int* thr, const int* eq, int* cursor, int factor,
-    int prefix_stages, int prefix_phase, int64_t capacity, int32_t* row_offset,
-    int32_t* row_counts, int32_t* stage_ids) {
-  extern __shared__ uint8_t code[];  // [R] precision code per column
-  __shared__ int warp_tot[kRowThreads / 32];
-  __shared__ int pre[3];
-  __shared__ int base_s;
-  const int row = blockIdx.x, head = blockIdx.y;
-  int key_b[3], quota_b[3];
+// One warp per row writes the row's list: NVFP4 columns, INT8 columns, FP16 columns, each
+// ascending, every logical block expanded to `factor` stages, prefix stages at the front of
+// the phase that carries them.
+__global__ void __launch_bounds__(kRowWarps * 32) emit_kernel(
+    const unsigned short* prob, int R, const int* thr, const int* stat, int factor,
+    int prefix_stages, int prefix_phase, int64_t capacity, const int32_t* row_offset,
+    const int32_t* row_counts, int32_t* stage_ids) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (row >= R) return;
+  const int lane = threadIdx.x & 31;
+  const unsigned lower = (1u << lane) - 1u;
+  int key_b[3], quota_b[3], run[3];
+  const int* st = stat + ((int64_t)head * R + row) * kStat;
 #pragma unroll
   for (int b = 0; b < 3; ++b) {
     key_b[b] = thr[head * 8 + 2 * b];
     quota_b[b] = thr[head * 8 + 2 * b + 1];
+    run[b] = st[3 + b];  // items of the straddling key in earlier rows
   }
-  // items of each straddling key in earlier rows
-  if (threadIdx.x < 3) pre[threadIdx.x] = 0;
-  __syncthreads();
-  {
-    int s0 = 0, s1 = 0, s2 = 0;
-    const int* e = eq + (int64_t)head * R * 4;
-    for (int r = threadIdx.x; r < row; r += kRowThreads) {
-      s0 += e[r * 4];
-      s1 += e[r * 4 + 1];
-      s2 += e[r * 4 + 2];
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      s0 += __shfl_xor_sync(0xffffffffu, s0, off);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, off);
-    }
-    if ((threadIdx.x & 31) == 0) {
-      atomicAdd(&pre[0], s0);
-      atomicAdd(&pre[1], s1);
-      atomicAdd(&pre[2], s2);
-    }
+  const int32_t* rc = row_counts + ((int64_t)head * R + row) * 4;
+  const int n0 = rc[0], n1 = rc[1], n2 = rc[2];
+  const int total = n0 + n1 + n2;
+  if (total == 0) return;
+  const int64_t base = row_offset[(int64_t)head * R + row];
+  if (base + total > capacity) return;  // cannot happen with exact budgets
+  int32_t* list = stage_ids + (int64_t)head * capacity + base;
+  const int p = prefix_phase >= 0 ? prefix_stages : 0;
+  // where the video stages of each phase start
+  int at[3] = {prefix_phase == 0 ? p : 0, n0 + (prefix_phase == 1 ? p : 0),
+               n0 + n1 + (prefix_phase == 2 ? p : 0)};
+  if (prefix_phase >= 0) {
+    const int seg = prefix_phase == 0 ? 0 : (prefix_phase == 1 ? n0 : n0 + n1);
+    for (int s = lane; s < p; s += 32) list[seg + s] = s;
   }
-  __syncthreads();
-  int run[3] = {pre[0], pre[1], pre[2]};
-  int count[3] = {0, 0, 0};  // per category 1,2,3 (uniform across the CTA)
   const unsigned short* src = prob + ((int64_t)head * R + row) * R;
-
-  for (int j0 = 0; j0 < R; j0 += kRowThreads) {
-    const int j = j0 + threadIdx.x;
+  for (int j0 = 0; j0 < R; j0 += 32) {
+    const int j = j0 + lane;
     const bool in = j < R;
     const int key = in ? (__ldg(src + j) & 0x7fff) : -2;
-    int t[3];
-#pragma unroll
-    for (int b = 0; b < 3; ++b) t[b] = ordered_rank(in && key == key_b[b], run[b], warp_tot);
     // rank < boundary b  <=>  key above the straddling key, or inside its bin before the quota
     bool below[3];
 #pragma unroll
-    for (int b = 0; b < 3; ++b) below[b] = key > key_b[b] || (key == key_b[b] && t[b] < quota_b[b]);
+    for (int b = 0; b < 3; ++b) {
+      const bool tie = in && key == key_b[b];
+      const unsigned ties = __ballot_sync(0xffffffffu, tie);
+      below[b] = key > key_b[b] || (tie && run[b] + __popc(ties & lower) < quota_b[b]);
+      run[b] += __popc(ties);
+    }
     const int c = !in ? 0 : (below[0] ? 3 : (below[1] ? 2 : (below[2] ? 1 : 0)));
-    if (in) code[j] = (uint8_t)c;
 #pragma unroll
     for (int k = 1; k <= 3; ++k) {
-      int dummy = 0;
-      (void)ordered_rank(c == k, dummy, warp_tot);
-      count[k - 1] += dummy;
-    }
-  }
-  __syncthreads();
-  const int p = prefix_phase >= 0 ? prefix_stages : 0;
-  const int total = (count[0] + count[1] + count[2]) * factor + p;
-  if (threadIdx.x == 0) {
-    const int off = total ? atomicAdd(cursor + head, total) : 0;
-    base_s = off;
-    row_offset[(int64_t)head * R + row] = off;
-    int32_t* rc = row_counts + ((int64_t)head * R + row) * 4;
-    rc[0] = count[0] * factor + (prefix_phase == 0 ? p : 0);
-    rc[1] = count[1] * factor + (prefix_phase == 1 ? p : 0);
-    rc[2] = count[2] * factor + (prefix_phase == 2 ? p : 0);
-    rc[3] = 0;
-  }
-  __syncthreads();
-  if (total == 0) return;
-  if ((int64_t)base_s + total > capacity) return;  // cannot happen with exact budgets
-  int32_t* list = stage_ids + (int64_t)head * capacity + base_s;
-  // segment starts (in stages) of the three phases
-  int seg[3];
-  seg[0] = 0;
-  seg[1] = count[0] * factor + (prefix_phase == 0 ? p : 0);
-  seg[2] = seg[1] + count[1] * factor + (prefix_phase == 1 ? p : 0);
-  if (prefix_phase >= 0)
-    for (int s = threadIdx.x; s < p; s += kRowThreads) list[seg[prefix_phase] + s] = s;
-  int placed[3] = {0, 0, 0};
-  for (int j0 = 0; j0 < R; j0 += kRowThreads) {
-    const int j = j0 + threadIdx.x;
-    const int c = j < R ? code[j] : 0;
-#pragma unroll
-    for (int k = 1; k <= 3; ++k) {
-      const int pos = ordered_rank(c == k, placed[k - 1], warp_tot);
+      const unsigned members = __ballot_sync(0xffffffffu, c == k);
       if (c == k) {
-        const int at = seg[k - 1] + (prefix_phase == k - 1 ? p : 0) + pos * factor;
-        for (int e = 0; e < factor; ++e) list[at + e] = prefix_stages + j * factor + e;
+        int32_t* dst = list + at[k - 1] + __popc(members & lower) * factor;
+        for (int e = 0; e < factor; ++e) dst[e] = prefix_stages + j * factor + e;
       }
+      at[k - 1] += __popc(members) * factor;
     }
-  }
-}
-
-// Launch order of a head's query blocks for the attention kernel: longest list first (ties by
-// block index), written as block + 1 into the fourth entry of row_counts, slot = position.
-// The last CTAs of a launch are then the short ones, which shortens the tail during which SMs
-// run out of work.  Blocks are ranked by counting (R^2 / threads comparisons per thread).
-constexpr int kOrderMaxBlocks = 4096;
-__global__ void __launch_bounds__(1024) order_kernel(int R, int32_t* row_counts) {
-  extern __shared__ int total[];
-  const int head = blockIdx.x;
-  int32_t* rc = row_counts + (int64_t)head * R * 4;
-  for (int i = threadIdx.x; i < R; i += blockDim.x) total[i] = rc[i * 4] + rc[i * 4 + 1] + rc[i * 4 + 2];
-  __syncthreads();
-  for (int i = threadIdx.x; i < R; i += blockDim.x) {
-    const int mine = total[i];
-    int rank = 0;
-    for (int j = 0; j < R; ++j) rank += (total[j] > mine) || (total[j] == mine && j < i);
-    rc[rank * 4 + 3] = i + 1;
   }
 }
 
@@ -311,29 +339,29 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
   RouteScratch sc;
   sc.hist = static_cast<int*>(scratch);
   sc.thr = sc.hist + (int64_t)H * kBins;
-  sc.eq = sc.thr + (int64_t)H * 8;
-  sc.cursor = sc.eq + (int64_t)H * R * 4;
-  if (cudaMemsetAsync(sc.hist, 0, (size_t)H * kBins * 4, st) != cudaSuccess ||
-      cudaMemsetAsync(sc.cursor, 0, (size_t)H * 4, st) != cudaSuccess)
+  sc.stat = sc.thr + (int64_t)H * 8;
+  if (cudaMemsetAsync(sc.hist, 0, (size_t)H * kBins * 4, st) != cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
   const unsigned short* prob = static_cast<const unsigned short*>(probability);
-  // Function attributes belong to a device: they are set at every call (two cheap host-side
-  // driver calls), so a process that routes on several GPUs, or from several host threads,
-  // never launches these kernels without the opt-in for their dynamic shared memory.
+  // Function attributes belong to a device: the opt-in is made at every call (a cheap host-side
+  // driver call), so a process that routes on several GPUs, or from several host threads,
+  // never launches the kernel without the opt-in for its dynamic shared memory.
   if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBins * 4) !=
-          cudaSuccess ||
-      cudaFuncSetAttribute(emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536) !=
-          cudaSuccess)
+      cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
-  const int chunks = (int)max((int64_t)1, min((int64_t)16, items / 32768));
+  // about two waves of histogram CTAs (one per SM: the bins fill its shared memory), each
+  // with at least 8192 items
+  const int chunks = (int)max((int64_t)1, min(min((int64_t)16, items / 8192), (int64_t)((296 + H / 2) / H)));
+  const int factor = shape->query_block / 64, prefix_stages = rec::prefix_stages(*shape);
+  const dim3 rows((R + kRowWarps - 1) / kRowWarps, H);
   hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, sc.hist);
   threshold_kernel<<<H, 1024, 0, st>>>(sc.hist, sc.thr, n16, n16 + n8, n16 + n8 + n4);
-  tally_kernel<<<dim3(R, H), kRowThreads, 0, st>>>(prob, R, sc.thr, sc.eq);
-  emit_kernel<<<dim3(R, H), kRowThreads, (size_t)((R + 15) & ~15), st>>>(
-      prob, R, sc.thr, sc.eq, sc.cursor, shape->query_block / 64, rec::prefix_stages(*shape),
-      prefix_phase, list_capacity, row_offset, row_counts, stage_ids);
-  // very large block counts keep the identity order (the fourth entries stay 0)
-  if (R <= kOrderMaxBlocks) order_kernel<<<H, 1024, (size_t)R * 4, st>>>(R, row_counts);
+  rowstat_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, R, sc.thr, sc.stat);
+  headscan_kernel<<<H, 1024, 0, st>>>(R, sc.thr, sc.stat, factor, prefix_stages, prefix_phase,
+                                      row_offset, row_counts);
+  emit_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, R, sc.thr, sc.stat, factor, prefix_stages,
+                                               prefix_phase, list_capacity, row_offset, row_counts,
+                                               stage_ids);
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
 
@@ -362,7 +390,7 @@ extern "C" int anemoi_sm100_route_static(const anemoi_sm100_shape* shape, const 
                                          void* stream) {
   if (rec::validate_shape(shape) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
   const int64_t need = scratch_ints(shape->heads, shape->video_blocks);
-  if (need > kStaticScratchInts) return ANEMOI_SM100_ELIMIT;  // heads*(32777 + 4*blocks) ints
+  if (need > kStaticScratchInts) return ANEMOI_SM100_ELIMIT;  // heads*(32776 + 6*blocks) ints
   int device = -1;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
     return ANEMOI_SM100_ELAUNCH;
@@ -376,8 +404,8 @@ extern "C" int anemoi_sm100_route_static(const anemoi_sm100_shape* shape, const 
       return ANEMOI_SM100_ELAUNCH;
     g_route_scratch_address[device] = scratch;
   }
-  // Same kernels as anemoi_sm100_route; the bins and cursors that must start at zero are
-  // cleared there on `stream` at every call, the rest is overwritten before it is read.
+  // Same kernels as anemoi_sm100_route; the bins that must start at zero are cleared there on
+  // `stream` at every call, the rest is overwritten before it is read.
   return anemoi_sm100_route(shape, probability, n16, n8, n4, prefix_phase, scratch, need * 4,
                             row_offset, row_counts, stage_ids, list_capacity, stream);
 }

@@ -248,7 +248,7 @@ def route(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_p
         stage_ids=torch.empty((h, max(cap, 1)), dtype=torch.int32, device=dev),
         capacity=max(cap, 1),
     )
-    _count("route", 5)                                  # hist, threshold, tally, emit, order
+    _count("route", 5)                                  # hist, threshold, rowstat, headscan, emit
     _check(lib.anemoi_sm100_route(C.byref(shape), _ptr(prob), n16, n8, n4, prefix_phase,
                                   _ptr(scratch), scratch.numel(), _ptr(lists.row_offset),
                                   _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,

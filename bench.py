@@ -575,7 +575,7 @@ def run_ours(args) -> None:
                              "per rank: copy in its sequence shard, Ulysses layer, copy out"),
                     "equals_device_resident_result": e2e_matches},
             # kernels of this library launched per step, counted by the ctypes layer as it calls them
-            # (v_amax, prepare, prefix attention, draft, hist, threshold, tally, emit, order,
+            # (v_amax, prepare, prefix attention, draft, hist, threshold, rowstat, headscan, emit,
             # attention, assemble; with N > 1 also pack and merge)
             "gpu_launches": launches,
             "stage_ms": stages,

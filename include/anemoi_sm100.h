@@ -119,7 +119,8 @@ int64_t anemoi_sm100_route_list_capacity(const anemoi_sm100_shape* shape, int64_
  *   probability  fp16 [H][R][R]
  *   n16,n8,n4    per-head budgets (FP16, INT8, NVFP4)
  *   prefix_phase -1 none, 0 nvfp4, 1 int8, 2 fp16: phase that carries the prefix stages
- *   row_offset   int32 [H][R]   start of the row's list inside the head's segment
+ *   row_offset   int32 [H][R]   start of the row's list inside the head's segment (the lists
+ *                follow one another in row order: the same layout at every call)
  *   row_counts   int32 [H][R][4] stages per phase (nvfp4, int8, fp16), prefix included; the
  *                fourth entry of slot i is 1 + the query block the attention kernel should run
  *                as its i-th CTA of the head (longest list first), or 0 for "block i"
@@ -141,7 +142,7 @@ int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* probability,
  * work with the same arguments and results, but its scratch is an 8 MiB array that is part
  * of the library image (held on every GPU that loads the library until the process ends);
  * it calls no allocating routine of any kind.  Shapes that need more scratch than that -
- * heads * (32777 + 4 * video_blocks) * 4 bytes > anemoi_sm100_route_static_max_bytes() -
+ * heads * (32776 + 6 * video_blocks) * 4 bytes > anemoi_sm100_route_static_max_bytes() -
  * are refused with ANEMOI_SM100_ELIMIT.  The first call on a device looks up the array's
  * device address; make that call outside any stream capture.  All calls on a device share
  * the one array (it keeps the last call's contents; what must start at zero is cleared on
