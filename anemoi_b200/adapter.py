@@ -204,6 +204,7 @@ class H3MPAAttention:
         self._sequence_seen: int | None = None
         self._mpa_before_request = 0
         self._closed = -1
+        self._device: torch.device | None = None      # where the sparse path last ran
 
     # ---- request / step tracking -------------------------------------------------------
     def observe(self, *, timestep: torch.Tensor | None, video_indices: torch.Tensor | None,
@@ -240,6 +241,18 @@ class H3MPAAttention:
         self.last_request_mpa_calls = self.mpa_calls - self._mpa_before_request
         self._mpa_before_request = self.mpa_calls
         self._closed = self.request
+        if self.last_request_mpa_calls > 0 and self._device is not None:
+            # The end of a request is a synchronisation point anyway: read the device's sticky
+            # status word there.  Non-zero means a bounded wait inside one of this device's
+            # kernels gave up during the request; the outputs of that call are not valid.
+            from . import executor
+
+            status = executor.last_status(self._device)
+            if status != 0:
+                raise RuntimeError(
+                    f"a kernel on {self._device} gave up a bounded wait during request {self.request} "
+                    f"(status {status}); its results are invalid. Call executor.reset_status() after "
+                    "handling the failure")
         if self.step + 1 <= self.config.dense_first_steps or self.last_request_mpa_calls > 0:
             return
         message = "request passed the dense-first schedule without an MPA call"
@@ -280,6 +293,7 @@ class H3MPAAttention:
     def mpa(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, layer: int) -> torch.Tensor:
         """Sparse mixed-precision attention of one layer (strided ``[S, H, D]`` views are fine)."""
         self._check(q, k, v)
+        self._device = q.device
         cfg = self.config
         if q.shape[0] != cfg.sequence_tokens:
             raise ValueError("packed sequence length does not match the H3 request")

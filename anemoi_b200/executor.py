@@ -41,6 +41,40 @@ def stage_times_ms() -> dict:
     return out
 
 
+_PROFILE_NVTX = False
+
+
+def set_profile_nvtx(enabled: bool) -> None:
+    """Process-wide switch for the NVTX ranges of every call (the per-call ``profile_nvtx``
+    argument turns them on for one call).  The ranges carry the reference's names
+    (anemoi/layers/attention/mpa/executor.py:901-902, 983-990, 1102, 1179, 1207):
+    ``anemoi.complete`` around the call and inside it ``anemoi.peripheral.prepare``,
+    ``anemoi.dense_prefix``, ``anemoi.peripheral.draft_route_materialize``, ``anemoi.mpa_mainloop``
+    and ``anemoi.peripheral.assembly``, so a timeline taken from either implementation reads
+    the same."""
+    global _PROFILE_NVTX
+    if type(enabled) is not bool:
+        raise TypeError("enabled must be a bool")
+    _PROFILE_NVTX = enabled
+
+
+class _Range:
+    """An NVTX range on the calling thread (host-side marker around the launches)."""
+
+    def __init__(self, name: str, enabled: bool):
+        self.name, self.enabled = name, enabled
+
+    def __enter__(self):
+        if self.enabled:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 class _Stage:
     """Brackets one native stage with CUDA events on the current stream when enabled."""
 
@@ -111,8 +145,26 @@ def sm100_ragged_attention(
     maxpool_weight: float = 0.0,
     nvfp4_scales: tuple[float, float, float] = (1.0, 1.0, 1.0),
     return_parts: bool = False,
+    profile_nvtx: bool = False,
 ):
     """Per-frame ragged Q64/Q128 routing and mixed-precision attention on sm_100a."""
+    if type(profile_nvtx) is not bool:
+        raise TypeError("profile_nvtx must be a bool")
+    with _Range("anemoi.complete", profile_nvtx or _PROFILE_NVTX):
+        return _ragged_attention(
+            q_bshd, k_bshd, v_bshd, prefix_tokens=prefix_tokens, sparsity_ratio=sparsity_ratio,
+            retained_nvfp4_ratio=retained_nvfp4_ratio, retained_int8_ratio=retained_int8_ratio,
+            retained_fp16_ratio=retained_fp16_ratio, video_shape=video_shape, layer=layer,
+            query_block_size=query_block_size, prefix_kv_precision=prefix_kv_precision,
+            prefix_query_precision=prefix_query_precision, maxpool_weight=maxpool_weight,
+            nvfp4_scales=nvfp4_scales, return_parts=return_parts,
+            nvtx=profile_nvtx or _PROFILE_NVTX)
+
+
+def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, retained_nvfp4_ratio,
+                      retained_int8_ratio, retained_fp16_ratio, video_shape, layer, query_block_size,
+                      prefix_kv_precision, prefix_query_precision, maxpool_weight, nvfp4_scales,
+                      return_parts, nvtx):
     if q_bshd.shape != k_bshd.shape or q_bshd.shape != v_bshd.shape:
         raise ValueError("Q/K/V must share [1,S,H,D], D in {64,128}")
     if (
@@ -160,7 +212,7 @@ def sm100_ragged_attention(
     if prefix_tokens and not native_prefix:
         # dense attention of the prefix rows on the caller's tensors, as the reference does
         side.wait_stream(current)
-        with torch.cuda.stream(side):
+        with torch.cuda.stream(side), _Range("anemoi.dense_prefix", nvtx):
             prefix_out = F.scaled_dot_product_attention(
                 q_bshd[:, :prefix_tokens].permute(0, 2, 1, 3),
                 k_bshd.permute(0, 2, 1, 3),
@@ -177,7 +229,7 @@ def sm100_ragged_attention(
                        native_prefix=native_prefix, has_maxpool=maxpool_weight != 0.0,
                        nvfp4_scales=nvfp4_scales)
     store = native.allocate_operands(shape, device)
-    with _Stage("prepare"):
+    with _Stage("prepare"), _Range("anemoi.peripheral.prepare", nvtx):
         native.prepare(shape, q_bshd, k_bshd, v_bshd, layout.indices, layout.counts, store)
     valid_k = _valid_k(device, prefix_tokens, query_block_size, _counts_key(layout))
     status = _status_word(device)
@@ -185,7 +237,7 @@ def sm100_ragged_attention(
     if native_prefix:
         side.wait_stream(current)
         with torch.cuda.stream(side):
-            with _Stage("prefix_attention"):
+            with _Stage("prefix_attention"), _Range("anemoi.dense_prefix", nvtx):
                 prefix_out = native.prefix_attention(shape, store, valid_k, status)
             for t in store.buffers.values():
                 if t is not None:
@@ -193,22 +245,23 @@ def sm100_ragged_attention(
             valid_k.record_stream(side)
             status.record_stream(side)
 
-    with _Stage("draft"):
-        prob = native.draft_probability(shape, store, float(maxpool_weight))
-    n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=float(sparsity_ratio),
-                               nvfp4_ratio=float(retained_nvfp4_ratio),
-                               int8_ratio=float(retained_int8_ratio),
-                               fp16_ratio=float(retained_fp16_ratio))
-    phase_index = -1 if prefix_phase is None else PHASE_ORDER.index(prefix_phase)
-    with _Stage("route"):
-        lists = native.route(shape, prob, n16, n8, n4, phase_index)
-    with _Stage("attention"):
+    with _Range("anemoi.peripheral.draft_route_materialize", nvtx):
+        with _Stage("draft"):
+            prob = native.draft_probability(shape, store, float(maxpool_weight))
+        n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=float(sparsity_ratio),
+                                   nvfp4_ratio=float(retained_nvfp4_ratio),
+                                   int8_ratio=float(retained_int8_ratio),
+                                   fp16_ratio=float(retained_fp16_ratio))
+        phase_index = -1 if prefix_phase is None else PHASE_ORDER.index(prefix_phase)
+        with _Stage("route"):
+            lists = native.route(shape, prob, n16, n8, n4, phase_index)
+    with _Stage("attention"), _Range("anemoi.mpa_mainloop", nvtx):
         packed = native.attention(shape, store, lists, valid_k, status)
 
     current.wait_stream(side)
     if prefix_out is not None:
         prefix_out.record_stream(current)
-    with _Stage("assemble"):
+    with _Stage("assemble"), _Range("anemoi.peripheral.assembly", nvtx):
         out = native.assemble(shape, prefix_out, packed, layout.inverse, lists.row_counts,
                               q_bshd.dtype)
     if return_parts:
@@ -304,4 +357,5 @@ def execute_ragged_attention(
     )
 
 
-__all__ = ["execute_ragged_attention", "sm100_ragged_attention", "last_status", "reset_status"]
+__all__ = ["execute_ragged_attention", "sm100_ragged_attention", "last_status", "reset_status",
+           "set_profile_nvtx"]

@@ -101,3 +101,24 @@ def test_pipelined_host_input_equals_the_single_call(native_library):
         runner(hq, hk, hv, hout, **kw)
         torch.cuda.synchronize()
         assert torch.equal(hout, want)
+
+
+def test_nvtx_ranges_do_not_change_the_result(native_library):
+    """The opt-in NVTX ranges (the reference's names) only mark the host timeline."""
+    from anemoi_b200 import executor
+
+    vs = (2, 10, 14)
+    q, k, v = (t.cuda() for t in smooth_fields(*vs, 2, 128, 37, seed=2, dtype=torch.bfloat16))
+    kw = dict(prefix_tokens=37, sparsity_ratio=0.5, retained_nvfp4_ratio=0.4, retained_int8_ratio=0.4,
+              retained_fp16_ratio=0.2, video_shape=vs, layer=0, query_block_size=64,
+              nvfp4_scales=(0.01, 0.01, 0.002))
+    plain = executor.sm100_ragged_attention(q, k, v, **kw)
+    marked = executor.sm100_ragged_attention(q, k, v, profile_nvtx=True, **kw)
+    executor.set_profile_nvtx(True)
+    try:
+        switched = executor.sm100_ragged_attention(q, k, v, **kw)
+    finally:
+        executor.set_profile_nvtx(False)
+    assert torch.equal(plain, marked) and torch.equal(plain, switched)
+    with pytest.raises(TypeError):
+        executor.sm100_ragged_attention(q, k, v, profile_nvtx=1, **kw)

@@ -359,3 +359,11 @@ def test_operand_sizes_and_argument_checks(native_library):
     assert native_library.anemoi_sm100_prepare(C.byref(s), None, None, None, None, None, None, None, None) == -1
     assert native_library.anemoi_sm100_route(C.byref(s), None, 1, 1, 1, 0, None, 0, None, None, None, 0, None) == -1
     assert native_library.anemoi_sm100_merge_heads(None, None, 4, 2, 2, 128, None) == -1
+
+
+def test_nvtx_switch_takes_only_bools():
+    from anemoi_b200 import executor
+
+    with pytest.raises(TypeError):
+        executor.set_profile_nvtx("yes")
+    executor.set_profile_nvtx(False)
