@@ -73,7 +73,10 @@ __global__ void __launch_bounds__(256) push_qkv_kernel(const uint16_t* q, const 
     const int lh = (int)(t % heads_local);
     t /= heads_local;
     const int64_t row = t % rows;
-    const int dest = (int)(t / rows);
+    // destinations in the order self+1, self+2, ..., self: at any moment the ranks of the node
+    // store to different destinations, instead of all into rank 0 first
+    int dest = self + 1 + (int)(t / rows);
+    dest -= dest >= ranks ? ranks : 0;
     const int gh = dest * heads_local + lh;
     const uint16_t* src = which == 0 ? q + row * qs_row + gh * qs_head
                         : which == 1 ? k + row * ks_row + gh * ks_head
@@ -92,16 +95,21 @@ __global__ void __launch_bounds__(256) push_out_kernel(const uint16_t* out_heads
                                                        int64_t total, uint32_t epoch,
                                                        unsigned int* blocks_done) {
   const int inner8 = heads_local * d8;
+  const int64_t total_rows = peers.first[ranks];
+  const int64_t row_shift = self + 1 < ranks ? peers.first[self + 1] : 0;
   for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * 256) {
     const int tail = (int)(idx % inner8);
-    const int64_t row = idx / inner8;
+    // rows starting with the next rank's shard (and wrapping), for the same reason
+    int64_t row = idx / inner8 + row_shift;
+    row -= row >= total_rows ? total_rows : 0;
     int owner = 0;
 #pragma unroll
     for (int r = 1; r < kMaxRanks; ++r) owner += (r < ranks && row >= peers.first[r]) ? 1 : 0;
     uint16_t* dst = peers.data[owner] +
                     (((row - peers.first[owner]) * ranks + self) * (int64_t)inner8 + tail) * 8;
-    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(out_heads) + idx);
+    *reinterpret_cast<uint4*>(dst) =
+        __ldg(reinterpret_cast<const uint4*>(out_heads) + row * inner8 + tail);
   }
   publish(peers, self, ranks, epoch, blocks_done);
 }

@@ -270,10 +270,15 @@ def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_de
     if world == 1:
         return attention_fn(q, k, v)
     if exchange is not None:
+        from .executor import _Stage
+
         d = q.size(3)
-        recv = exchange.to_heads(q[0], k[0], v[0])
+        with _Stage("exchange_to_heads"):
+            recv = exchange.to_heads(q[0], k[0], v[0])
         qh, kh, vh = (recv[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
-        return exchange.to_sequence(attention_fn(qh, kh, vh)[0].contiguous()).unsqueeze(0)
+        result = attention_fn(qh, kh, vh)[0].contiguous()
+        with _Stage("exchange_to_sequence"):
+            return exchange.to_sequence(result).unsqueeze(0)
     rank = dist.get_rank(group)
     rows, heads, d = q.size(1), q.size(2), q.size(3)
     if heads % world:
