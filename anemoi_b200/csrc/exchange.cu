@@ -19,6 +19,7 @@
 #include <stdint.h>
 
 #include "../../include/anemoi_sm100.h"
+#include "norm_rope.cuh"
 
 namespace {
 
@@ -84,6 +85,54 @@ __global__ void __launch_bounds__(256) push_qkv_kernel(const uint16_t* q, const 
     uint16_t* dst = peers.data[dest] +
                     ((((row0 + row) * heads_local + lh) * 3 + which) * (int64_t)d8 + c8) * 8;
     *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src) + c8);
+  }
+  publish(peers, self, ranks, epoch, blocks_done);
+}
+
+// The same exchange with the producer step in it: q and k get the per-head RMS norm with weight
+// and the partial rotary embedding (norm_rope.cuh: the arithmetic of the stand-alone producer
+// kernel, bit for bit) on their way from the projection output to the peers, v passes through.
+// The normalised q and k are never written to this rank's memory: the in-place producer pass
+// (one read and one write of q and k) disappears.  The D/8 lanes of a (row, head) are
+// consecutive threads; whole warps stay in the loop because the lanes of a row shuffle.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) push_qkv_norm_kernel(
+    const uint16_t* q, const uint16_t* k, const uint16_t* v, const T* q_weight, const T* k_weight,
+    const float* cos_table, const float* sin_table, int rotary_dim, float eps, PeerTable peers,
+    int self, int ranks, int64_t rows, int heads_local, int64_t total, int64_t qs_row,
+    int64_t qs_head, int64_t ks_row, int64_t ks_head, int64_t vs_row, int64_t vs_head,
+    uint32_t epoch, unsigned int* blocks_done) {
+  constexpr int d8 = D / 8;
+  const int64_t row0 = peers.first[self];
+  const int lane_in_warp = threadIdx.x & 31;
+  for (int64_t base = (int64_t)blockIdx.x * 256 + (threadIdx.x - lane_in_warp); base < total;
+       base += (int64_t)gridDim.x * 256) {
+    const int64_t idx = base + lane_in_warp;
+    const bool live = idx < total;
+    const int c8 = (int)(idx % d8);
+    int64_t t = idx / d8;
+    const int which = (int)(t % 3);
+    t /= 3;
+    const int lh = (int)(t % heads_local);
+    t /= heads_local;
+    const int64_t row = live ? t % rows : 0;
+    int dest = self + 1 + (live ? (int)(t / rows) : 0);
+    dest -= dest >= ranks ? ranks : 0;
+    const int gh = dest * heads_local + lh;
+    const uint16_t* src = which == 0 ? q + row * qs_row + gh * qs_head
+                        : which == 1 ? k + row * ks_row + gh * ks_head
+                                     : v + row * vs_row + gh * vs_head;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = __ldg(reinterpret_cast<const uint4*>(src) + c8);
+    // q and k rows go through the producer arithmetic (every lane calls: the row's lanes shuffle)
+    const uint4 done = nr::norm_rope8<T, D>(raw, which == 1 ? k_weight : q_weight,
+                                            cos_table + row * rotary_dim, sin_table + row * rotary_dim,
+                                            rotary_dim, eps, c8, live && which < 2);
+    if (live) {
+      uint16_t* dst = peers.data[dest] +
+                      ((((row0 + row) * heads_local + lh) * 3 + which) * (int64_t)d8 + c8) * 8;
+      *reinterpret_cast<uint4*>(dst) = which < 2 ? done : raw;
+    }
   }
   publish(peers, self, ranks, epoch, blocks_done);
 }
@@ -236,5 +285,57 @@ extern "C" int anemoi_sm100_wait_flags(const void* flags, int32_t ranks, uint32_
     return ANEMOI_SM100_EINVAL;
   wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint32_t*>(flags), ranks, epoch, limit_ns, status);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
+
+namespace {
+template <typename T, int D>
+void launch_norm(const void* q, const void* k, const void* v, const void* qw, const void* kw,
+                 const float* c, const float* sn, int rotary, float eps, const PeerTable& t, int self,
+                 int ranks, int64_t rows, int heads_local, int64_t total, const int64_t* strides,
+                 uint32_t epoch, void* blocks_done, cudaStream_t st) {
+  const int blocks = (int)max((int64_t)1, min((total + 255) / 256, (int64_t)(148 * 16)));
+  push_qkv_norm_kernel<T, D><<<blocks, 256, 0, st>>>(
+      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(k), static_cast<const uint16_t*>(v),
+      static_cast<const T*>(qw), static_cast<const T*>(kw), c, sn, rotary, eps, t, self, ranks,
+      max(rows, (int64_t)1), heads_local, total, strides[0], strides[1], strides[2], strides[3],
+      strides[4], strides[5], epoch, static_cast<unsigned int*>(blocks_done));
+}
+}  // namespace
+
+extern "C" int anemoi_sm100_push_qkv_norm(const void* q, const void* k, const void* v,
+                                          const void* q_weight, const void* k_weight,
+                                          const float* cos_table, const float* sin_table,
+                                          int32_t rotary_dim, float eps, int32_t is_bf16,
+                                          void* const* peer_recv, void* const* peer_flags,
+                                          const int64_t* first_rows, int32_t self, int32_t ranks,
+                                          int32_t heads, int32_t head_dim, const int64_t* strides,
+                                          uint32_t epoch, void* blocks_done, void* stream) {
+  if (!peer_recv || !peer_flags || !first_rows || !strides || !blocks_done || !q_weight ||
+      !k_weight || ranks <= 0 || ranks > kMaxRanks || self < 0 || self >= ranks || heads <= 0 ||
+      heads % ranks || (head_dim != 64 && head_dim != 128))
+    return ANEMOI_SM100_EINVAL;
+  if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 16 || !(eps >= 0.0f))
+    return ANEMOI_SM100_EINVAL;
+  for (int i = 0; i < 6; ++i)
+    if (strides[i] % 8) return ANEMOI_SM100_EINVAL;
+  PeerTable t{};
+  if (int rc = fill(t, peer_recv, peer_flags, first_rows, ranks, false)) return rc;
+  const int64_t rows = first_rows[self + 1] - first_rows[self];
+  // a rank without rows has no tensors and no table rows
+  if (rows > 0 && (!q || !k || !v)) return ANEMOI_SM100_EINVAL;
+  if (rows > 0 && rotary_dim > 0 && (!cos_table || !sin_table)) return ANEMOI_SM100_EINVAL;
+  const int heads_local = heads / ranks;
+  const int64_t total = (int64_t)ranks * rows * heads_local * 3 * (head_dim / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define ANEMOI_LAUNCH_NORM(T, D)                                                                  \
+  launch_norm<T, D>(q, k, v, q_weight, k_weight, cos_table, sin_table, rotary_dim, eps, t, self,  \
+                    ranks, rows, heads_local, total, strides, epoch, blocks_done, st)
+  if (is_bf16) {
+    if (head_dim == 64) ANEMOI_LAUNCH_NORM(__nv_bfloat16, 64); else ANEMOI_LAUNCH_NORM(__nv_bfloat16, 128);
+  } else {
+    if (head_dim == 64) ANEMOI_LAUNCH_NORM(__half, 64); else ANEMOI_LAUNCH_NORM(__half, 128);
+  }
+#undef ANEMOI_LAUNCH_NORM
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }

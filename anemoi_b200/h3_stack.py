@@ -72,12 +72,14 @@ class H3BlockStack:
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
 
     def step(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, attention_fn, *, norm_rope,
-             group=None, pack=None, merge=None, on_attention=None, exchange=None) -> torch.Tensor:
+             group=None, pack=None, merge=None, on_attention=None, exchange=None,
+             fuse_producer: bool = False) -> torch.Tensor:
         """One denoising step: every block in turn.  ``attention_fn(q, k, v)`` takes the
         head-sharded ``[S, h, D]`` tensors of a layer; ``norm_rope(x, weight, cos, sin, eps)`` is the
         producer fusion (in place, ``[1, rows, heads, D]``); ``on_attention(begin)`` is called with
         True / False around the exchange + attention of each layer (timing hook); ``exchange`` is an
-        optional ``ulysses.PeerExchange`` (stores into the peers' memory instead of all-to-alls)."""
+        optional ``ulysses.PeerExchange`` (stores into the peers' memory instead of all-to-alls);
+        with ``fuse_producer`` the producer fusion is folded into that exchange's stores."""
         c = self.config
         rows = x.size(0)
         kw = {}
@@ -91,12 +93,18 @@ class H3BlockStack:
             q = (h @ blk["wq"]).view(1, rows, c.heads, c.head_dim)
             k = (h @ blk["wk"]).view(1, rows, c.heads, c.head_dim)
             v = (h @ blk["wv"]).view(1, rows, c.heads, c.head_dim)
-            norm_rope(q, blk["qn"], cos, sin, c.eps)
-            norm_rope(k, blk["kn"], cos, sin, c.eps)
+            producer = {}
+            if exchange is not None and fuse_producer:
+                # qk-norm + rotary ride on the exchange's stores: no in-place pass over q and k
+                producer = dict(producer=(blk["qn"], blk["kn"], cos, sin, c.eps))
+            else:
+                norm_rope(q, blk["qn"], cos, sin, c.eps)
+                norm_rope(k, blk["kn"], cos, sin, c.eps)
             if on_attention is not None:
                 on_attention(True)
             attn = ulysses.ulysses_attention(
-                q, k, v, lambda qh, kh, vh: attention_fn(qh[0], kh[0], vh[0]).unsqueeze(0), group, **kw)
+                q, k, v, lambda qh, kh, vh: attention_fn(qh[0], kh[0], vh[0]).unsqueeze(0), group, **kw,
+                **producer)
             if on_attention is not None:
                 on_attention(False)
             x = x + gate1 * (attn.reshape(rows, c.inner) @ blk["wo"])

@@ -100,6 +100,9 @@ def library() -> C.CDLL:
         "anemoi_sm100_peer_free": (C.c_int, [P]),
         "anemoi_sm100_push_qkv": (C.c_int, [P, P, P, C.POINTER(P), C.POINTER(P), C.POINTER(I64), I32, I32, I32,
                                             I32, C.POINTER(I64), C.c_uint32, P, P]),
+        "anemoi_sm100_push_qkv_norm": (C.c_int, [P, P, P, P, P, P, P, I32, C.c_float, I32, C.POINTER(P),
+                                                 C.POINTER(P), C.POINTER(I64), I32, I32, I32, I32,
+                                                 C.POINTER(I64), C.c_uint32, P, P]),
         "anemoi_sm100_push_out": (C.c_int, [P, C.POINTER(P), C.POINTER(P), C.POINTER(I64), I32, I32, I32, I32,
                                             C.c_uint32, P, P]),
         "anemoi_sm100_wait_flags": (C.c_int, [P, I32, C.c_uint32, C.c_uint64, P, P]),
@@ -133,7 +136,7 @@ EXPORTED = (
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
     "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
     "anemoi_sm100_wait_selftest", "anemoi_sm100_copy_rows", "anemoi_sm100_push_qkv",
-    "anemoi_sm100_push_out", "anemoi_sm100_wait_flags", "anemoi_sm100_peer_alloc", "anemoi_sm100_peer_open",
+    "anemoi_sm100_push_qkv_norm", "anemoi_sm100_push_out", "anemoi_sm100_wait_flags", "anemoi_sm100_peer_alloc", "anemoi_sm100_peer_open",
     "anemoi_sm100_peer_close", "anemoi_sm100_peer_free",
 )
 
@@ -423,10 +426,15 @@ def peer_free(ptr: int) -> None:
     _check(library().anemoi_sm100_peer_free(C.c_void_p(ptr)), "anemoi_sm100_peer_free")
 
 
-def push_qkv(q, k, v, peer_recv, peer_flags, first_rows, rank: int, epoch: int, blocks_done) -> None:
+def push_qkv(q, k, v, peer_recv, peer_flags, first_rows, rank: int, epoch: int, blocks_done,
+             producer=None) -> None:
     """Store this rank's rows of ``q, k, v`` ``(rows, heads, D)`` into every rank's head-sharded
     receive buffer ``(all rows, heads/world, 3*D)`` and publish ``epoch`` in their flag words;
-    ``peer_recv`` / ``peer_flags`` hold the addresses as mapped into this process."""
+    ``peer_recv`` / ``peer_flags`` hold the addresses as mapped into this process.
+
+    ``producer = (q_weight, k_weight, cos, sin, eps)`` applies the per-head RMS norm and partial
+    rotary embedding of ``fused_qknorm_rope`` to q and k on the way (``cos``/``sin``: fp32
+    ``(rows, rotary_dim)``); the caller's q and k are left as they are."""
     world = len(peer_recv)
     rows, heads, d = q.shape
     if rows != first_rows[rank + 1] - first_rows[rank]:
@@ -436,6 +444,19 @@ def push_qkv(q, k, v, peer_recv, peer_flags, first_rows, rank: int, epoch: int, 
     first = (C.c_int64 * (world + 1))(*first_rows)
     strides = (C.c_int64 * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
     _count("push_qkv", 1)
+    if producer is not None:
+        wq, wk, cos, sin, eps = producer
+        rotary = int(cos.shape[-1])
+        if (wq.dtype != q.dtype or wk.dtype != q.dtype or cos.dtype != torch.float32 or sin.dtype != torch.float32
+                or not cos.is_contiguous() or not sin.is_contiguous() or cos.shape != (rows, rotary)
+                or sin.shape != cos.shape or wq.numel() != d or wk.numel() != d):
+            raise ValueError("producer needs (D,) weights of the tensors' dtype and contiguous fp32 "
+                             "(rows, rotary_dim) cos / sin tables")
+        _check(library().anemoi_sm100_push_qkv_norm(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), _ptr(cos), _ptr(sin), rotary, float(eps),
+            int(q.dtype == torch.bfloat16), data, flags, first, rank, world, heads, d, strides,
+            epoch & 0xFFFFFFFF, _ptr(blocks_done), _stream(q.device)), "anemoi_sm100_push_qkv_norm")
+        return
     _check(library().anemoi_sm100_push_qkv(_ptr(q), _ptr(k), _ptr(v), data, flags, first, rank, world, heads, d,
                                            strides, epoch & 0xFFFFFFFF, _ptr(blocks_done), _stream(q.device)),
            "anemoi_sm100_push_qkv")

@@ -207,14 +207,16 @@ class PeerExchange:
         self.epoch, self.inbound = 0, False
         dist.barrier(group=group)                # every region is mapped before anyone stores
 
-    def to_heads(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        """``(rows_local, H, D)`` x3 -> ``(S, H/world, 3*D)``: this rank's heads of every row."""
+    def to_heads(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, producer=None) -> torch.Tensor:
+        """``(rows_local, H, D)`` x3 -> ``(S, H/world, 3*D)``: this rank's heads of every row.
+        ``producer = (q_weight, k_weight, cos, sin, eps)`` folds the qk-norm + partial rotary step
+        into the stores (``native.push_qkv``)."""
         if self.inbound:
             raise RuntimeError("to_heads called twice without to_sequence in between")
         self.epoch += 1
         self.inbound = True
         native.push_qkv(q, k, v, self.recv_ptrs, self.flags_in, self.first, self.rank, self.epoch,
-                        self.blocks_done)
+                        self.blocks_done, producer)
         native.wait_flags(self.flags_in[self.rank], self.world, self.epoch, self.limit_ns, self.status,
                           self.device)
         return self.recv
@@ -249,7 +251,7 @@ class PeerExchange:
 
 def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_destination_major,
                       merge=native.merge_heads, pipeline_groups: int = 1,
-                      exchange: PeerExchange | None = None):
+                      exchange: PeerExchange | None = None, producer=None):
     """Head-shard, run ``attention_fn(q, k, v)`` on ``[1, S, h, D]`` views, shard back.
 
     ``q, k, v``: ``[1, rows_local, H, D]`` (this rank's rows, every head).  Returns
@@ -265,8 +267,12 @@ def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_de
     8.2 ms per layer) than the overlap wins; on 2 GPUs two groups are 0.5 % faster.
 
     With ``exchange`` (a ``PeerExchange`` built once for this shape and group) both all-to-alls
-    and their pack / merge copies are replaced by stores into the peers' memory."""
+    and their pack / merge copies are replaced by stores into the peers' memory; ``producer =
+    (q_weight, k_weight, cos, sin, eps)`` then also folds the qk-norm + partial rotary step that
+    precedes the exchange into those stores (q and k are passed as the projections wrote them)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if producer is not None and (world == 1 or exchange is None):
+        raise ValueError("the producer step is folded into the peer exchange only (world > 1, exchange=...)")
     if world == 1:
         return attention_fn(q, k, v)
     if exchange is not None:
@@ -274,7 +280,7 @@ def ulysses_attention(q, k, v, attention_fn, group=None, pack=native.pack_qkv_de
 
         d = q.size(3)
         with _Stage("exchange_to_heads"):
-            recv = exchange.to_heads(q[0], k[0], v[0])
+            recv = exchange.to_heads(q[0], k[0], v[0], producer)
         qh, kh, vh = (recv[..., i * d : (i + 1) * d].unsqueeze(0) for i in range(3))
         result = attention_fn(qh, kh, vh)[0].contiguous()
         with _Stage("exchange_to_sequence"):

@@ -716,7 +716,7 @@ def run_dit_step(args) -> None:
     def one_step(timestep: float):
         attention.observe(timestep=torch.tensor(timestep), video_indices=None, position_ids=position_ids)
         return stack.step(x, cos, sin, attention, norm_rope=fused_qknorm_rope, on_attention=on_attention,
-                          exchange=exchange)
+                          exchange=exchange, fuse_producer=exchange is not None and not args.no_fused_producer)
 
     def barrier():
         if world > 1:
@@ -761,6 +761,8 @@ def run_dit_step(args) -> None:
                                    f"dense attention in the first {args.dit_dense_layers} layers, sparse "
                                    "NVFP4/INT8/FP16 40/40/20 at 80% drop elsewhere",
                        "parallelism": f"ulysses{world}" if world > 1 else "single", "exchange": exchange_kind,
+                       "producer": "inside the exchange's stores" if exchange is not None and not args.no_fused_producer
+                                   else "in-place kernel before the exchange",
                        "dense_calls": stats["dense_calls"], "mpa_calls": stats["mpa_calls"]},
             "clocks": clocks.summary()}))
     if exchange is not None:
@@ -867,6 +869,9 @@ def main() -> None:
     ap.add_argument("--exchange", choices=("auto", "peer", "nccl"), default="auto",
                     help="N > 1: Ulysses exchange by stores into the peers' memory, by NCCL all-to-all, or "
                          "the first if its set-up succeeds on every rank")
+    ap.add_argument("--no-fused-producer", action="store_true",
+                    help="dit-step with the peer exchange: run qk-norm + rotary as its own in-place kernel "
+                         "instead of inside the exchange's stores")
     ap.add_argument("--pipeline-groups", type=int, default=1,
                     help="head groups whose exchange is pipelined under the attention (N > 1)")
     ap.add_argument("--config", choices=("layer", "dit-step"), default="layer",

@@ -257,6 +257,19 @@ int anemoi_sm100_push_qkv(const void* q, const void* k, const void* v, void* con
                           void* const* peer_flags, const int64_t* first_rows, int32_t self,
                           int32_t ranks, int32_t heads, int32_t head_dim, const int64_t* strides,
                           uint32_t epoch, void* blocks_done, void* stream);
+/* push_qkv with the producer step in it: q and k get the per-head RMS norm with weight and the
+ * partial rotary embedding of anemoi_sm100_qknorm_rope (same arithmetic, bit for bit; `cos_table`,
+ * `sin_table` fp32 [rows][rotary_dim] for this rank's rows) on their way to the peers, v passes
+ * through; q and k of the caller stay as the projection wrote them.  Replaces, fused with the
+ * collective, fused_qknorm_rope + pack + all_to_all_single of the reference
+ * (optimized/ulysses_custom.py:237-249 and :107-135). */
+int anemoi_sm100_push_qkv_norm(const void* q, const void* k, const void* v, const void* q_weight,
+                               const void* k_weight, const float* cos_table, const float* sin_table,
+                               int32_t rotary_dim, float eps, int32_t is_bf16,
+                               void* const* peer_recv, void* const* peer_flags,
+                               const int64_t* first_rows, int32_t self, int32_t ranks, int32_t heads,
+                               int32_t head_dim, const int64_t* strides, uint32_t epoch,
+                               void* blocks_done, void* stream);
 int anemoi_sm100_push_out(const void* out_heads, void* const* peer_out, void* const* peer_flags,
                           const int64_t* first_rows, int32_t self, int32_t ranks,
                           int32_t heads_local, int32_t head_dim, uint32_t epoch, void* blocks_done,

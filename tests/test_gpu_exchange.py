@@ -79,3 +79,51 @@ def test_flag_wait_gives_up_with_the_late_rank_in_the_status_word(native_library
     native.wait_flags(flags.data_ptr(), 2, 0xFFFFFFFF, 300_000, status, dev)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,heads,dim,rotary", [((37, 36), 4, 128, 64), ((9, 8, 8, 8), 8, 64, 32),
+                                                     ((5, 0, 4), 3, 128, 128)])
+def test_push_with_the_producer_step_equals_producer_then_push(native_library, counts, heads, dim, rotary, dtype):
+    """qk-norm + partial rotary folded into the exchange's stores give, bit for bit, what the
+    in-place producer kernel followed by the plain push gives; v passes through, and the caller's
+    q and k are left as the projections wrote them."""
+    from anemoi_b200 import native
+    from anemoi_b200.producer import fused_qknorm_rope
+    from anemoi_b200.ulysses import first_rows
+
+    world, first = len(counts), first_rows(list(counts))
+    total, h_local = first[-1], heads // len(counts)
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(3)
+    wide = [torch.randn(c, heads, 3 * dim, generator=gen, device=dev).to(dtype) for c in counts]
+    qkv = [[w[..., i * dim:(i + 1) * dim] for i in range(3)] for w in wide]
+    wq = (1 + 0.1 * torch.randn(dim, generator=gen, device=dev)).to(dtype)
+    wk = (1 + 0.1 * torch.randn(dim, generator=gen, device=dev)).to(dtype)
+    angle = [torch.rand(c, rotary, generator=gen, device=dev) * 6.2832 for c in counts]
+    cos, sin = [a.cos().contiguous() for a in angle], [a.sin().contiguous() for a in angle]
+    ptrs = lambda ts: [t.data_ptr() for t in ts]          # noqa: E731
+
+    def run(fused: bool):
+        recv = [torch.full((total, h_local, 3 * dim), float("nan"), dtype=dtype, device=dev) for _ in range(world)]
+        flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(world)]
+        done = torch.zeros(1, dtype=torch.int32, device=dev)
+        for r in range(world):
+            q, k, v = qkv[r]
+            if fused:
+                before = wide[r].clone()
+                native.push_qkv(q, k, v, ptrs(recv), ptrs(flags), first, r, 1, done,
+                                (wq, wk, cos[r], sin[r], 1e-6))
+                assert torch.equal(wide[r], before)
+            else:
+                q, k = q.contiguous(), k.contiguous()
+                if counts[r]:
+                    fused_qknorm_rope(q[None], wq, cos[r], sin[r], 1e-6)
+                    fused_qknorm_rope(k[None], wk, cos[r], sin[r], 1e-6)
+                native.push_qkv(q, k, v, ptrs(recv), ptrs(flags), first, r, 1, done)
+        torch.cuda.synchronize()
+        assert all(int(f[:world].min()) == 1 for f in flags)
+        return recv
+
+    for a, b in zip(run(True), run(False)):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))

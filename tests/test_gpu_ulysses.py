@@ -42,6 +42,22 @@ def _worker(rank, world, port, results):
                 torch.cuda.synchronize()
                 ok = ok and bool(torch.equal(got, full[:, lo : lo + rows[rank]]))
             ok = ok and last_status(torch.device("cuda", rank)) == 0
+            # the producer step folded into the exchange equals the in-place kernel before it
+            from anemoi_b200.producer import fused_qknorm_rope
+
+            gen = torch.Generator().manual_seed(9)
+            wq, wk = ((1 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16).cuda() for _ in range(2))
+            angle = torch.rand(q.size(1), 64, generator=gen) * 6.2832
+            cos, sin = (f(angle)[lo : lo + rows[rank]].contiguous().cuda() for f in (torch.cos, torch.sin))
+            qn, kn = mine[0].clone(), mine[1].clone()
+            fused_qknorm_rope(qn, wq, cos, sin, 1e-6)
+            fused_qknorm_rope(kn, wk, cos, sin, 1e-6)
+            want = ulysses.ulysses_anemoi_attention(qn, kn, mine[2], exchange=peer, **kw)
+            want = want.clone()
+            local = lambda a, b, c: anemoi_attention(a, b, c, **kw)          # noqa: E731
+            got = ulysses.ulysses_attention(*mine, local, exchange=peer, producer=(wq, wk, cos, sin, 1e-6))
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(got, want))
         finally:
             peer.close()
         results[rank] = ok
