@@ -78,6 +78,11 @@ struct AttnParams {
   const int32_t* stage_ids;
   int64_t capacity;
   const int32_t* valid_k;
+  // Q64 pairs: query blocks 2t and 2t+1 of a head share one CTA (rows 0-63 and 64-127 of the
+  // 128-row MMA shape) and walk the union of their lists; bits 30 / 31 of a list entry say which
+  // of the two blocks the stage belongs to.  Null: one query block per CTA.
+  const int32_t* pair_counts;  // [H][ceil(R/2)][4]
+  const int32_t* pair_ids;     // [H][capacity], a pair's list starts at row_offset of block 2t
   __half* out;       // [H][tiles*QB][D]
   int32_t* status;
   uint64_t wait_ns;  // limit of every mbarrier wait
@@ -230,6 +235,13 @@ __device__ __forceinline__ void write_p(uint8_t* p_tile, int row, const float (&
   }
 }
 
+// A row of zeros in the P tile (a stage that does not belong to this row's query block).
+__device__ __forceinline__ void write_zero_p(uint8_t* p_tile, int row, int cell) {
+  const int chunks = cell == kF16 ? 8 : (cell == kI8 ? 4 : 2);
+  for (int j = 0; j < chunks; ++j)
+    *reinterpret_cast<uint4*>(p_tile + rec::tile_offset(row, j, chunks)) = make_uint4(0, 0, 0, 0);
+}
+
 // Bytes of one P tile (128 rows x 64 keys) per cell, and which of the two buffers stage g uses.
 __device__ __forceinline__ int p_tile_bytes(int cell) {
   return cell == kNv ? 128 * 32 : (cell == kI8 ? 128 * 64 : 128 * 128);
@@ -246,9 +258,10 @@ template <int D>
 __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, uint8_t* p_smem,
                                               const float* colf, uint32_t tmem_row, int row,
                                               int cell, int g, bool phase_first,
-                                              float score_scale, int valid, bool live_warp, int sb,
-                                              uint32_t s_parity, uint64_t* prev_pv_bar,
-                                              uint32_t prev_pv_parity, RowState& st) {
+                                              float score_scale, int valid, bool live_warp,
+                                              bool member, int sb, uint32_t s_parity,
+                                              uint64_t* prev_pv_bar, uint32_t prev_pv_parity,
+                                              RowState& st) {
   wait(&b->wc, &b->s_full[sb], s_parity, 10 + cell);
   tc_fence_after_sync();
   // Barrier arrivals are one per warp (lane 0 after a warp sync).
@@ -259,6 +272,26 @@ __device__ __forceinline__ void softmax_stage(Barriers* b, const AttnParams& p, 
       if (cell == kNv) mbar_arrive(&b->s_free);
       mbar_arrive(&b->p_full[g & 1]);
     }
+    return;
+  }
+  if (!member) {
+    // A stage of the other query block of the pair (warp-uniform: a warp's rows belong to one
+    // block).  These rows contribute nothing: P = 0, running maximum and denominator untouched.
+    // O still has to change its value domain at the first stage of a phase.
+    if (cell == kNv) {
+      __syncwarp();
+      if (lead) mbar_arrive(&b->s_free);
+    }
+    if (g > 0 && (phase_first || cell == kF16)) {
+      wait(&b->wc, prev_pv_bar, prev_pv_parity, 20 + cell);
+      tc_fence_after_sync();
+      if (phase_first) rescale_o<D, true>(tmem_row, 1.0f, colf);
+    }
+    write_zero_p(p_smem + p_buffer(cell, g) * p_tile_bytes(cell), row, cell);
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lead) mbar_arrive(&b->p_full[g & 1]);
     return;
   }
   float s[64];
@@ -451,20 +484,42 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
   // launch order of the head's query blocks (longest list first) as written by the routing
   // stage; 0 = no order given
   int tile = blockIdx.x;
+  const bool pairs = p.pair_counts != nullptr;
+  const int pair_tiles = (p.s.video_blocks + 1) / 2;
   if (!p.dense_prefix) {
-    const int ordered = p.row_counts[((int64_t)head * p.s.video_blocks + blockIdx.x) * 4 + 3];
+    const int ordered =
+        pairs ? p.pair_counts[((int64_t)head * pair_tiles + blockIdx.x) * 4 + 3]
+              : p.row_counts[((int64_t)head * p.s.video_blocks + blockIdx.x) * 4 + 3];
     if (ordered > 0) tile = ordered - 1;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // query blocks of this CTA (two for a complete pair) and the first one's index
+  const int tile_blocks = pairs && 2 * tile + 1 < p.s.video_blocks ? 2 : 1;
+  const int block0 = pairs ? 2 * tile : tile;
 
   // ---- this tile's work list ----
   int cnt[3];
+  int first_of[3] = {0, 0, 0};  // where each phase starts inside the list
   const int32_t* list;
   if (p.dense_prefix) {
     cnt[0] = 0;
     cnt[1] = p.stages;
     cnt[2] = 0;
     list = nullptr;
+  } else if (pairs) {
+    const int32_t* pc = p.pair_counts + ((int64_t)head * pair_tiles + tile) * 4;
+    cnt[0] = pc[0];
+    cnt[1] = pc[1];
+    cnt[2] = pc[2];
+    // phase c of the union sits where the two blocks' phases before it would end
+    const int32_t* ra = p.row_counts + ((int64_t)head * p.s.video_blocks + block0) * 4;
+    int before = 0;
+    for (int c = 0; c < 3; ++c) {
+      first_of[c] = before;
+      before += ra[c] + (tile_blocks == 2 ? ra[4 + c] : 0);
+    }
+    list = p.pair_ids + (int64_t)head * p.capacity +
+           p.row_offset[(int64_t)head * p.s.video_blocks + block0];
   } else {
     const int32_t* rc = p.row_counts + ((int64_t)head * p.s.video_blocks + tile) * 4;
     cnt[0] = rc[0];
@@ -472,6 +527,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     cnt[2] = rc[2];
     list = p.stage_ids + (int64_t)head * p.capacity +
            p.row_offset[(int64_t)head * p.s.video_blocks + tile];
+    first_of[1] = cnt[0];
+    first_of[2] = cnt[0] + cnt[1];
   }
   const int total = cnt[0] + cnt[1] + cnt[2];
   if (total == 0) return;
@@ -515,9 +572,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
   tc_fence_after_sync();
   const uint32_t tmem = b->tmem_base;
 
-  const int q_index_fp = head * p.s.video_blocks + tile;  // q_fp16 / q_nvfp4 record
+  const int q_index_fp = head * p.s.video_blocks + block0;  // q_fp16 / q_nvfp4 record
   const int64_t q_index_i8 =
-      (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : tile);
+      (int64_t)head * p.q_tiles_int8 + (p.dense_prefix ? p.s.video_blocks + tile : block0);
   const float sigma = (D == 64 ? 0.125f : 0.08838834764831845f) * 1.4426950408889634f;
 
   // The second warpgroup (loader, MMA and two idle warps) hands most of its registers to the
@@ -539,14 +596,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
           cell == kNv ? static_cast<const uint8_t*>(p.o.q_nvfp4) + (int64_t)q_index_fp * qbytes
           : cell == kI8 ? static_cast<const uint8_t*>(p.o.q_int8) + q_index_i8 * qbytes
                         : static_cast<const uint8_t*>(p.o.q_fp16) + (int64_t)q_index_fp * qbytes;
-      mbar_arrive_expect_tx(&b->q_full, qbytes, lead);
+      mbar_arrive_expect_tx(&b->q_full, qbytes * tile_blocks, lead);
       if (cell == kNv && QB == 64) {
-        // codes fill the first half of the 128-row tile; scale blocks follow the full tile
+        // codes fill the first half of the 128-row tile; scale blocks follow the full tile.
+        // A pair's second record: codes into the second half of the tile, scale blocks behind
+        // the first record's (the MMA warp folds them into one block before it copies them).
         const int codes = QB * D / 2;
         bulk_g2s(q_smem, qsrc, codes, &b->q_full, lead);
         bulk_g2s(q_smem + 128 * D / 2, qsrc + codes, qbytes - codes, &b->q_full, lead);
+        if (tile_blocks == 2) {
+          bulk_g2s(q_smem + codes, qsrc + qbytes, codes, &b->q_full, lead);
+          bulk_g2s(q_smem + 128 * D / 2 + (qbytes - codes), qsrc + qbytes + codes, qbytes - codes,
+                   &b->q_full, lead);
+        }
       } else {
-        bulk_g2s(q_smem, qsrc, qbytes, &b->q_full, lead);
+        // records of consecutive query blocks follow one another: two make a 128-row tile
+        bulk_g2s(q_smem, qsrc, qbytes * tile_blocks, &b->q_full, lead);
       }
       const int kvbytes = CellInfo<D>::kv_bytes(cell);
       const uint8_t* kvbase =
@@ -554,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
            : cell == kI8 ? static_cast<const uint8_t*>(p.o.kv_int8)
                          : static_cast<const uint8_t*>(p.o.kv_fp16)) +
           (int64_t)head * p.stages * kvbytes;
-      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      const int first = first_of[cell];
       // The ring is cut into equal slots of this phase's record size; slots of the
       // previous phase must all be released before the new geometry is written.
       const int slot_bytes = (kvbytes + 127) & ~127;
@@ -567,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       for (int i = 0; i < cnt[cell]; ++i) {
         if ((i & 31) == 0 && list != nullptr && i + lane < cnt[cell])
           stage_l = list[first + i + lane];
-        const int stage = list ? __shfl_sync(0xffffffffu, stage_l, i & 31) : i;
+        const int stage = list ? (__shfl_sync(0xffffffffu, stage_l, i & 31) & 0x3fffffff) : i;
         slot = slot + 1 == nslot ? 0 : slot + 1;
         if ((filled >> slot) & 1u)
           wait<kPark>(&b->wc, &b->kv_free[slot], ((fillpar >> slot) & 1u) ^ 1u, 2);
@@ -592,6 +657,19 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
       wait<kPark>(&b->wc, &b->q_full, phase_ord & 1, 3);
       tc_fence_after_sync();
       if (cell == kNv) {
+        if (tile_blocks == 2) {
+          // Scale bytes of rows 0-63 sit in the low eight bytes of every 16-byte chunk, those of
+          // rows 64-127 in the high eight.  Both records hold their 64 rows in the low halves:
+          // the second record's move up into the first record's empty high halves.
+          uint8_t* sfa = q_smem + 128 * D / 2;
+          const uint8_t* sfb = sfa + (D / 64) * 512;
+          for (int c = lane; c < (D / 64) * 32; c += 32) {
+            const uint2 lo = *reinterpret_cast<const uint2*>(sfb + c * 16);
+            *reinterpret_cast<uint2*>(sfa + c * 16 + 8) = lo;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
         const uint32_t qsf = q_addr + 128 * D / 2;
 #pragma unroll
         for (int k = 0; k < D / 64; ++k)
@@ -652,7 +730,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     int prev_cell = -1;
     const float nv_dom = p.s.v_global_scale * (1.0f / (6.0f * 448.0f));
     const float* vscale = p.o.v_e4m3_scale ? p.o.v_e4m3_scale + (int64_t)head * D : nullptr;
-    const bool live_warp = warp * 32 < QB;
+    const bool live_warp = warp * 32 < QB * tile_blocks;
+    const int my_block = warp * 32 >= QB && tile_blocks == 2 ? 1 : 0;  // which block of a pair
     if (cnt[kNv] > 0) {
       tmem_st4(tmem_row + kColSfaP, 0x7e7e7e7eu);  // constant 448 block scale of P
       tmem_wait_st();
@@ -670,15 +749,16 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         }
         asm volatile("bar.sync 5, 128;" ::: "memory");
       }
-      const int first = cell == 0 ? 0 : (cell == 1 ? cnt[0] : cnt[0] + cnt[1]);
+      const int first = first_of[cell];
       const float q_scale =
-          cell == kI8 ? p.o.q_int8_scale[q_index_i8] : 1.0f;
+          cell == kI8 ? p.o.q_int8_scale[q_index_i8 + my_block] : 1.0f;
       const float base_scale =
           cell == kNv ? sigma * p.s.q_global_scale * p.s.k_global_scale : sigma;
       // Per-stage metadata (stage id -> real keys, key scale) is fetched 32 stages at a
       // time, one stage per lane, and handed out with shuffles: no dependent global
       // loads sit on the per-stage critical path.
       int meta_valid = 64;
+      int meta_member = 1;
       float meta_scale = 1.0f;
       const int nslot = min(kMaxSlots, p.ring_bytes / ((CellInfo<D>::kv_bytes(cell) + 127) & ~127));
       const float* kscale = cell == kI8 ? p.o.k_int8_scale + (int64_t)head * p.stages : nullptr;
@@ -687,12 +767,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         if ((i & 31) == 0) {
           const int mine = i + lane;
           if (mine < cnt[cell]) {
-            const int stage = list ? list[first + mine] : mine;
+            const int entry = list ? list[first + mine] : mine;
+            const int stage = entry & 0x3fffffff;
+            if (pairs) meta_member = (entry >> (30 + my_block)) & 1;
             meta_valid = p.valid_k[stage];
             if (cell == kI8) meta_scale = sigma * (q_scale * kscale[stage]);
           }
         }
         const int valid = __shfl_sync(0xffffffffu, meta_valid, i & 31);
+        const bool member = !pairs || __shfl_sync(0xffffffffu, meta_member, i & 31) != 0;
         const bool phase_first = i == 0 && prev_cell >= 0;
         const int sb = s_buffer(cell, g);
         const uint32_t s_parity = (sb ? s_use1 : s_use0) & 1;
@@ -708,7 +791,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
         const float sc =
             cell == kI8 ? __shfl_sync(0xffffffffu, meta_scale, i & 31) : base_scale;
         softmax_stage<D>(b, p, p_smem, colf, tmem_row, row, cell, g, phase_first, sc, valid,
-                         live_warp, sb, s_parity, pv_bar, pv_parity, st);
+                         live_warp, member, sb, s_parity, pv_bar, pv_parity, st);
       }
       prev_cell = cell;
     }
@@ -716,9 +799,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const AttnParams
     wait(&b->wc, &b->all_done, 0, 7);
     if (live_warp) {
       tc_fence_after_sync();
-      const float inv = 1.0f / st.d;
-      const bool live = row < QB;
-      __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)tile * QB + row) * D;
+      // a block of a pair may have an empty list of its own: its rows are never read
+      const float inv = st.d > 0.0f ? 1.0f / st.d : 0.0f;
+      const bool live = row < QB * tile_blocks;
+      __half* dst = p.out + ((int64_t)head * p.out_rows + (int64_t)block0 * QB + row) * D;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t r[32];
@@ -759,7 +843,8 @@ int launch(AttnParams& p, int tiles, cudaStream_t st) {
   int q_region = 0, p_region = 0, slot = 0;
   const bool nv = p.s.has_nvfp4 && !p.dense_prefix, f16 = p.s.has_fp16 && !p.dense_prefix;
   if (nv) {
-    q_region = max(q_region, 128 * D / 2 + (D / 64) * 512);
+    // a pair of Q64 blocks brings a second set of scale blocks
+    q_region = max(q_region, 128 * D / 2 + (D / 64) * 512 * (p.pair_counts ? 2 : 1));
     p_region = max(p_region, 2 * 128 * 32);
     slot = max(slot, (int)rec::kv_nvfp4_bytes(D));
   }
@@ -837,13 +922,13 @@ extern "C" int anemoi_sm100_wait_selftest(uint64_t limit_ns, int32_t* status, vo
   return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }
 
-extern "C" int anemoi_sm100_attention(const anemoi_sm100_shape* shape,
-                                      const anemoi_sm100_operands* ops, const int32_t* row_offset,
-                                      const int32_t* row_counts, const int32_t* stage_ids,
-                                      int64_t list_capacity, const int32_t* valid_k,
-                                      void* out_packed, int32_t* status, void* stream) {
+namespace {
+int video_attention(const anemoi_sm100_shape* shape, const anemoi_sm100_operands* ops,
+                    const int32_t* row_offset, const int32_t* row_counts, const int32_t* stage_ids,
+                    const int32_t* pair_counts, const int32_t* pair_ids, int64_t list_capacity,
+                    const int32_t* valid_k, void* out_packed, int32_t* status, void* stream) {
   if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !ops || !row_offset || !row_counts ||
-      !stage_ids || !valid_k || !out_packed || !status || list_capacity <= 0)
+      !valid_k || !out_packed || !status || list_capacity <= 0)
     return ANEMOI_SM100_EINVAL;
   if (check_ops(*shape, *ops, false) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
   AttnParams p{};
@@ -852,6 +937,8 @@ extern "C" int anemoi_sm100_attention(const anemoi_sm100_shape* shape,
   p.row_offset = row_offset;
   p.row_counts = row_counts;
   p.stage_ids = stage_ids;
+  p.pair_counts = pair_counts;
+  p.pair_ids = pair_ids;
   p.capacity = list_capacity;
   p.valid_k = valid_k;
   p.out = static_cast<__half*>(out_packed);
@@ -861,9 +948,31 @@ extern "C" int anemoi_sm100_attention(const anemoi_sm100_shape* shape,
   p.stages = rec::stages(*shape);
   p.q_tiles_int8 = shape->video_blocks + rec::prefix_query_tiles(*shape);
   p.out_rows = shape->video_blocks * shape->query_block;
+  const int tiles = pair_counts ? (shape->video_blocks + 1) / 2 : shape->video_blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return shape->head_dim == 64 ? launch<64>(p, shape->video_blocks, st)
-                               : launch<128>(p, shape->video_blocks, st);
+  return shape->head_dim == 64 ? launch<64>(p, tiles, st) : launch<128>(p, tiles, st);
+}
+}  // namespace
+
+extern "C" int anemoi_sm100_attention(const anemoi_sm100_shape* shape,
+                                      const anemoi_sm100_operands* ops, const int32_t* row_offset,
+                                      const int32_t* row_counts, const int32_t* stage_ids,
+                                      int64_t list_capacity, const int32_t* valid_k,
+                                      void* out_packed, int32_t* status, void* stream) {
+  if (!stage_ids) return ANEMOI_SM100_EINVAL;
+  return video_attention(shape, ops, row_offset, row_counts, stage_ids, nullptr, nullptr,
+                         list_capacity, valid_k, out_packed, status, stream);
+}
+
+extern "C" int anemoi_sm100_attention_pairs(const anemoi_sm100_shape* shape,
+                                            const anemoi_sm100_operands* ops,
+                                            const int32_t* row_offset, const int32_t* row_counts,
+                                            const int32_t* pair_counts, const int32_t* pair_ids,
+                                            int64_t list_capacity, const int32_t* valid_k,
+                                            void* out_packed, int32_t* status, void* stream) {
+  if (!pair_counts || !pair_ids || !shape || shape->query_block != 64) return ANEMOI_SM100_EINVAL;
+  return video_attention(shape, ops, row_offset, row_counts, nullptr, pair_counts, pair_ids,
+                         list_capacity, valid_k, out_packed, status, stream);
 }
 
 extern "C" int anemoi_sm100_prefix_attention(const anemoi_sm100_shape* shape,

@@ -20,6 +20,7 @@
 // layout is the same at every call) and the launch order follow without touching
 // the map again; a last pass per row writes the lists.  The per-row passes use one
 // warp per row: ranks inside a row come from ballots, no block-wide barrier.
+#include <climits>
 #include <cuda_fp16.h>
 
 #include "records.cuh"
@@ -302,7 +303,84 @@ __global__ void __launch_bounds__(kRowWarps * 32) emit_kernel(
   }
 }
 
+// Q64 query blocks 2t and 2t+1 of a head run as one CTA of the attention kernel (rows 0-63 and
+// 64-127 of the 128-row MMA shape).  That CTA walks, phase by phase, the union of the two
+// blocks' lists; bits 30 and 31 of an entry say which of the two blocks the stage belongs to.
+// One warp per pair, one lane per phase (a two-pointer merge of two ascending lists).  The union
+// of phase c is written where the two blocks' phases before c would end, inside the space the two
+// lists occupy in the stage list (a buffer of the same capacity), so no offsets are scanned.
+// The pairs of a head are then ranked longest first, like the blocks.
+__global__ void __launch_bounds__(kRowWarps * 32) pair_kernel(int R, int64_t capacity,
+                                                              const int32_t* row_offset,
+                                                              const int32_t* row_counts,
+                                                              const int32_t* stage_ids,
+                                                              int32_t* pair_counts,
+                                                              int32_t* pair_ids) {
+  const int pairs = (R + 1) / 2;
+  const int pair = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const int a = 2 * pair;
+  const bool has_b = a + 1 < R;
+  const int32_t* ca = row_counts + ((int64_t)head * R + a) * 4;
+  const int64_t base = row_offset[(int64_t)head * R + a];
+  const int32_t* la = stage_ids + (int64_t)head * capacity + base;
+  const int32_t* lb = la + (ca[0] + ca[1] + ca[2]);  // lists follow one another in row order
+  int32_t* out = pair_ids + (int64_t)head * capacity + base;
+  int n = 0;
+  if (lane < 3) {
+    int sa = 0, sb = 0, so = 0;  // starts of this lane's phase in A, in B and in the union
+    for (int c = 0; c < lane; ++c) {
+      sa += ca[c];
+      sb += has_b ? ca[4 + c] : 0;
+    }
+    so = sa + sb;
+    const int na = ca[lane], nb = has_b ? ca[4 + lane] : 0;
+    int i = 0, j = 0;
+    while (i < na || j < nb) {
+      const int x = i < na ? la[sa + i] : INT_MAX;
+      const int y = j < nb ? lb[sb + j] : INT_MAX;
+      const int v = min(x, y);
+      out[so + n++] = v | (x == v ? 1 << 30 : 0) | (y == v ? (int)(1u << 31) : 0);
+      i += x == v;
+      j += y == v;
+    }
+  }
+  if (lane < 4) pair_counts[((int64_t)head * pairs + pair) * 4 + lane] = lane < 3 ? n : 0;
+}
+
+// Launch order of a head's pairs: longest union first (ties by pair index), as for the blocks.
+__global__ void __launch_bounds__(1024) pair_order_kernel(int pairs, int32_t* pair_counts) {
+  __shared__ int total_s[kOrderMaxBlocks];
+  const int head = blockIdx.x;
+  int32_t* pc = pair_counts + (int64_t)head * pairs * 4;
+  for (int i = threadIdx.x; i < pairs; i += 1024) total_s[i] = pc[i * 4] + pc[i * 4 + 1] + pc[i * 4 + 2];
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += 1024) {
+    const int mine = total_s[i];
+    int rank = 0;
+    for (int j = 0; j < pairs; ++j) rank += (total_s[j] > mine) || (total_s[j] == mine && j < i);
+    pc[rank * 4 + 3] = i + 1;
+  }
+}
+
 }  // namespace
+
+extern "C" int anemoi_sm100_pair_lists(const anemoi_sm100_shape* shape, const int32_t* row_offset,
+                                       const int32_t* row_counts, const int32_t* stage_ids,
+                                       int64_t list_capacity, int32_t* pair_counts,
+                                       int32_t* pair_ids, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !row_offset || !row_counts || !stage_ids ||
+      !pair_counts || !pair_ids || list_capacity <= 0 || shape->query_block != 64)
+    return ANEMOI_SM100_EINVAL;
+  if (rec::stages(*shape) >= (1 << 30)) return ANEMOI_SM100_ELIMIT;  // two flag bits per entry
+  const int R = shape->video_blocks, H = shape->heads, pairs = (R + 1) / 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  pair_kernel<<<dim3((pairs + kRowWarps - 1) / kRowWarps, H), kRowWarps * 32, 0, st>>>(
+      R, list_capacity, row_offset, row_counts, stage_ids, pair_counts, pair_ids);
+  if (pairs <= kOrderMaxBlocks) pair_order_kernel<<<H, 1024, 0, st>>>(pairs, pair_counts);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
 
 extern "C" int64_t anemoi_sm100_route_scratch_bytes(const anemoi_sm100_shape* shape) {
   if (rec::validate_shape(shape) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;

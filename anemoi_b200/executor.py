@@ -42,6 +42,7 @@ def stage_times_ms() -> dict:
 
 
 _PROFILE_NVTX = False
+_PAIR_Q64 = True      # Q64 query blocks run two per CTA; False keeps one (padded) block per CTA
 
 
 def set_profile_nvtx(enabled: bool) -> None:
@@ -256,7 +257,9 @@ def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, 
         with _Stage("route"):
             lists = native.route(shape, prob, n16, n8, n4, phase_index)
     with _Stage("attention"), _Range("anemoi.mpa_mainloop", nvtx):
-        packed = native.attention(shape, store, lists, valid_k, status)
+        # Q64: two query blocks per CTA fill the 128-row MMA shape and walk the union of their lists
+        pairs = native.pair_lists(shape, lists) if query_block_size == 64 and _PAIR_Q64 else None
+        packed = native.attention(shape, store, lists, valid_k, status, pairs)
 
     current.wait_stream(side)
     if prefix_out is not None:

@@ -92,6 +92,8 @@ def library() -> C.CDLL:
         "anemoi_sm100_route_static_max_bytes": (I64, []),
         "anemoi_sm100_route_static": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, P, I64, P]),
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
+        "anemoi_sm100_attention_pairs": (C.c_int, [SP, OP, P, P, P, P, I64, P, P, P, P]),
+        "anemoi_sm100_pair_lists": (C.c_int, [SP, P, P, P, I64, P, P, P]),
         "anemoi_sm100_prefix_attention": (C.c_int, [SP, OP, P, P, P, P]),
         "anemoi_sm100_copy_rows": (C.c_int, [P, I64, P, I64, I64, I64, I32, P]),
         "anemoi_sm100_peer_alloc": (C.c_int, [I64, C.POINTER(P), P]),
@@ -132,6 +134,7 @@ EXPORTED = (
     "anemoi_sm100_draft_probability", "anemoi_sm100_route_scratch_bytes",
     "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
+    "anemoi_sm100_attention_pairs", "anemoi_sm100_pair_lists",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
     "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
@@ -274,12 +277,40 @@ def route_static(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, p
         "anemoi_sm100_route_static")
 
 
+@dataclass
+class PairLists:
+    """Union lists of the Q64 query-block pairs (2t, 2t+1) of every head."""
+    pair_counts: torch.Tensor  # int32 [H, ceil(R/2), 4]: stages per phase of the union, launch order
+    pair_ids: torch.Tensor     # int32 [H, capacity]: stage id | membership bits 30 (block 2t), 31 (2t+1)
+
+
+def pair_lists(shape: Shape, lists: RouteLists) -> PairLists:
+    """Merges the lists of query blocks 2t and 2t+1 (Q64 only) for ``attention(..., pairs=)``."""
+    dev = lists.stage_ids.device
+    pairs = PairLists(
+        pair_counts=torch.empty((shape.heads, (shape.video_blocks + 1) // 2, 4), dtype=torch.int32, device=dev),
+        pair_ids=torch.empty_like(lists.stage_ids))
+    _count("pair_lists", 2)                              # merge, launch order
+    _check(library().anemoi_sm100_pair_lists(
+        C.byref(shape), _ptr(lists.row_offset), _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,
+        _ptr(pairs.pair_counts), _ptr(pairs.pair_ids), _stream(dev)), "anemoi_sm100_pair_lists")
+    return pairs
+
+
 def attention(shape: Shape, store: OperandStore, lists: RouteLists, valid_k: torch.Tensor,
-              status: torch.Tensor) -> torch.Tensor:
+              status: torch.Tensor, pairs: PairLists | None = None) -> torch.Tensor:
+    """The video query blocks' attention.  With ``pairs`` (Q64) two query blocks share a CTA and
+    walk the union of their lists; the result is the same."""
     dev = valid_k.device
     out = torch.empty((shape.heads, shape.video_blocks * shape.query_block, shape.head_dim),
                       dtype=torch.float16, device=dev)
     _count("attention", 1)
+    if pairs is not None:
+        _check(library().anemoi_sm100_attention_pairs(
+            C.byref(shape), C.byref(store.struct), _ptr(lists.row_offset), _ptr(lists.row_counts),
+            _ptr(pairs.pair_counts), _ptr(pairs.pair_ids), lists.capacity, _ptr(valid_k), _ptr(out),
+            _ptr(status), _stream(dev)), "anemoi_sm100_attention_pairs")
+        return out
     _check(library().anemoi_sm100_attention(
         C.byref(shape), C.byref(store.struct), _ptr(lists.row_offset), _ptr(lists.row_counts),
         _ptr(lists.stage_ids), lists.capacity, _ptr(valid_k), _ptr(out), _ptr(status),

@@ -178,6 +178,27 @@ int anemoi_sm100_set_wait_limit_ns(uint64_t limit_ns);
  * kernel returns normally. */
 int anemoi_sm100_wait_selftest(uint64_t limit_ns, int32_t* status, void* stream);
 
+/* Q64 only: query blocks 2t and 2t+1 of a head as one CTA (rows 0-63 and 64-127 of the 128-row MMA
+ * shape), walking phase by phase the union of their two lists.  pair_lists merges the lists:
+ *   pair_counts  int32 [H][ceil(R/2)][4]  stages per phase of the union; fourth entry = launch order
+ *   pair_ids     int32 [H][capacity]      stage id, bit 30: belongs to block 2t, bit 31: to 2t+1;
+ *                a pair's list starts at row_offset of block 2t, phase c of the union where the
+ *                two blocks' phases before c would end
+ * attention_pairs is anemoi_sm100_attention over those lists; rows of a block ignore the stages
+ * of the other one (zero probabilities, running maximum and denominator untouched), so every
+ * row sees exactly its own stages in its own order and the result is that of anemoi_sm100_attention.
+ * The reference runs one 64-row block per CTA with 16 rows per warp
+ * (sm120/q64_attention.cuh:1109-1390); the pairing exists because the tcgen05 shape is 128 rows. */
+int anemoi_sm100_pair_lists(const anemoi_sm100_shape* shape, const int32_t* row_offset,
+                            const int32_t* row_counts, const int32_t* stage_ids,
+                            int64_t list_capacity, int32_t* pair_counts, int32_t* pair_ids,
+                            void* stream);
+int anemoi_sm100_attention_pairs(const anemoi_sm100_shape* shape, const anemoi_sm100_operands* ops,
+                                 const int32_t* row_offset, const int32_t* row_counts,
+                                 const int32_t* pair_counts, const int32_t* pair_ids,
+                                 int64_t list_capacity, const int32_t* valid_k, void* out_packed,
+                                 int32_t* status, void* stream);
+
 /* Dense INT8-cell attention of the prefix query rows over every stage.
  *   out_prefix   fp16 [H][prefix query tiles * QB][D]
  * Replaces sm120_q{64,128}_prefix_int8_attention_forward

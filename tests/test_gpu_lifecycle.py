@@ -122,3 +122,29 @@ def test_nvtx_ranges_do_not_change_the_result(native_library):
     assert torch.equal(plain, marked) and torch.equal(plain, switched)
     with pytest.raises(TypeError):
         executor.sm100_ragged_attention(q, k, v, profile_nvtx=1, **kw)
+
+
+@pytest.mark.parametrize("vs,dim,prefix,cell,drop", [
+    ((2, 10, 14), 64, 0, (0.4, 0.4, 0.2), 0.5),        # 6 blocks
+    ((3, 9, 21), 128, 37, (0.4, 0.4, 0.2), 0.6),       # 9 blocks: the last pair has one block
+    ((4, 16, 16), 64, 0, (0.0, 1.0, 0.0), 0.8),
+    ((3, 9, 21), 128, 70, (1.0, 0.0, 0.0), 0.5),
+    ((4, 16, 16), 128, 0, (0.5, 0.0, 0.5), 0.97),      # blocks with empty lists inside pairs
+])
+def test_q64_pairs_equal_one_block_per_cta(native_library, vs, dim, prefix, cell, drop):
+    """Two Q64 query blocks per CTA walking the union of their lists give, bit for bit, what one
+    (padded) block per CTA gives: every row meets exactly its own stages in its own order."""
+    from anemoi_b200 import executor
+
+    q, k, v = (t.cuda() for t in smooth_fields(*vs, 3, dim, prefix, seed=7, outliers=(5, 41),
+                                               dtype=torch.bfloat16))
+    paired = _call(q, k, v, vs, prefix, cell, drop, 64)
+    executor._PAIR_Q64 = False
+    try:
+        single = _call(q, k, v, vs, prefix, cell, drop, 64)
+    finally:
+        executor._PAIR_Q64 = True
+    torch.cuda.synchronize()
+    assert torch.isfinite(paired).all()
+    assert torch.equal(paired, single)
+    assert executor.last_status() == 0
