@@ -134,6 +134,118 @@ __device__ __forceinline__ void row_stats(const __half* lg, int R, float& mx, fl
   inv = __fdiv_rn(1.0f, s);
 }
 
+// ---- diag-Jensen variant (an experimental routing proxy of the reference,
+// anemoi/layers/attention/mpa/routing.py:87-103) -------------------------------------------
+//   logit = q.k/sqrt(D) + 0.5 * max((q2.k2 - (q*q).(k*k)) / D, 0)   in fp32, not rounded to fp16
+// q2, k2: per-channel second moments of the blocks.  Three dot products per pair, each the same
+// channel-ordered FMA chain as above (two rows per warp, four key columns per lane); the third
+// one's inputs are the fp32 squares of the pools.  kStep 0: base = round(acc * scale) stored;
+// 1: v = acc stored in the second buffer; 2: logit = fma(0.5, max((v - acc) / D, 0), base).
+template <int D, int kStep>
+__device__ __forceinline__ void jensen_pass(const __half* q_src, const __half* k_src, int head, int R,
+                                            int row0, float* kc, float* qs, float* lg, float* var,
+                                            int stride) {
+  constexpr int kRows = kWarps * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float scale = D == 64 ? 0.125f : __int_as_float(0x3db504f3);
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kRows * D; idx += kWarps * 32) {
+    const int r = idx / D, c = idx % D;
+    const int row = row0 + r;
+    float x = row < R ? __half2float(q_src[((int64_t)head * R + row) * D + c]) : 0.0f;
+    if (kStep == 2) x = __fmul_rn(x, x);
+    qs[((r >> 1) * D + c) * 2 + (r & 1)] = x;
+  }
+  for (int c0 = 0; c0 < R; c0 += kChunk) {
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const float* qw = qs + warp * D * 2;
+    for (int s0 = 0; s0 < D; s0 += kSlab) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < kChunk * (kSlab / 8); idx += kWarps * 32) {
+        const int col = idx % kChunk, c8 = idx / kChunk;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (c0 + col < R)
+          raw = __ldg(reinterpret_cast<const uint4*>(k_src + ((int64_t)head * R + c0 + col) * D + s0) + c8);
+        const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float x = __half2float(h[i]);
+          if (kStep == 2) x = __fmul_rn(x, x);
+          kc[(c8 * 8 + i) * kPitch + col] = x;
+        }
+      }
+      __syncthreads();
+#pragma unroll 4
+      for (int c = 0; c < kSlab; ++c) {
+        const float2 qv = *reinterpret_cast<const float2*>(qw + (s0 + c) * 2);
+        const float4 kv = *reinterpret_cast<const float4*>(kc + c * kPitch + lane * 4);
+        acc[0][0] = __fmaf_rn(qv.x, kv.x, acc[0][0]);
+        acc[0][1] = __fmaf_rn(qv.x, kv.y, acc[0][1]);
+        acc[0][2] = __fmaf_rn(qv.x, kv.z, acc[0][2]);
+        acc[0][3] = __fmaf_rn(qv.x, kv.w, acc[0][3]);
+        acc[1][0] = __fmaf_rn(qv.y, kv.x, acc[1][0]);
+        acc[1][1] = __fmaf_rn(qv.y, kv.y, acc[1][1]);
+        acc[1][2] = __fmaf_rn(qv.y, kv.z, acc[1][2]);
+        acc[1][3] = __fmaf_rn(qv.y, kv.w, acc[1][3]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = c0 + lane * 4 + j;
+        if (col >= R) continue;
+        const int at = (warp * 2 + r) * stride + col;
+        if (kStep == 0) {
+          lg[at] = __fmul_rn(acc[r][j], scale);
+        } else if (kStep == 1) {
+          var[at] = acc[r][j];
+        } else {
+          const float t = fmaxf(__fmul_rn(__fsub_rn(var[at], acc[r][j]), 1.0f / D), 0.0f);
+          lg[at] = __fmaf_rn(0.5f, t, lg[at]);
+        }
+      }
+  }
+  __syncwarp();
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32) draft_jensen_kernel(const __half* q_pool,
+                                                                   const __half* k_pool,
+                                                                   const __half* q_second,
+                                                                   const __half* k_second, int R,
+                                                                   __half* prob) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  constexpr int kRows = kWarps * 2;
+  const int stride = (R + 3) & ~3;
+  float* kc = reinterpret_cast<float*>(smem_raw);  // [kSlab][kPitch]
+  float* qs = kc + kSlab * kPitch;                 // [kWarps][D][2]
+  float* lg = qs + kRows * D;                      // [kRows][stride] fp32 logits
+  float* var = lg + kRows * stride;                // [kRows][stride]
+  const int head = blockIdx.y, row0 = blockIdx.x * kRows;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  jensen_pass<D, 0>(q_pool, k_pool, head, R, row0, kc, qs, lg, var, stride);
+  jensen_pass<D, 1>(q_second, k_second, head, R, row0, kc, qs, lg, var, stride);
+  jensen_pass<D, 2>(q_pool, k_pool, head, R, row0, kc, qs, lg, var, stride);
+  for (int r = 0; r < 2; ++r) {
+    const int row = row0 + warp * 2 + r;
+    if (row >= R) break;
+    const float* mine = lg + (warp * 2 + r) * stride;
+    float m = -INFINITY;
+    for (int j = lane; j < R; j += 32) m = fmaxf(m, mine[j]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float sum = 0.0f;
+    for (int j = lane; j < R; j += 32) sum = __fadd_rn(sum, exp_canonical(__fsub_rn(mine[j], m)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
+    const float inv = __fdiv_rn(1.0f, sum);
+    __half* out = prob + ((int64_t)head * R + row) * R;
+    for (int j = lane; j < R; j += 32)
+      out[j] = __float2half_rn(__fmul_rn(exp_canonical(__fsub_rn(mine[j], m)), inv));
+  }
+}
+
 template <int D, bool kBlend, int RPW>
 __global__ void __launch_bounds__(kWarps * 32) draft_kernel(const __half* q_pool,
                                                             const __half* k_pool,
@@ -238,4 +350,36 @@ extern "C" int anemoi_sm100_draft_probability(const anemoi_sm100_shape* shape, c
                  : launch<64, false>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st);
   return blend ? launch<128, true>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st)
                : launch<128, false>(qp, kp, qx, kx, maxpool_weight, R, H, prob, st);
+}
+
+extern "C" int anemoi_sm100_draft_probability_jensen(const anemoi_sm100_shape* shape,
+                                                     const void* q_pool, const void* k_pool,
+                                                     const void* q_second, const void* k_second,
+                                                     void* probability, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !q_pool || !k_pool || !q_second || !k_second ||
+      !probability)
+    return ANEMOI_SM100_EINVAL;
+  const int R = shape->video_blocks, H = shape->heads, D = shape->head_dim;
+  const size_t smem = (size_t)kSlab * kPitch * 4 + (size_t)kWarps * 2 * D * 4 +
+                      (size_t)kWarps * 2 * ((R + 3) & ~3) * 4 * 2;
+  if (smem > 227 * 1024) return ANEMOI_SM100_ELIMIT;  // two fp32 row buffers: R up to about 1,400
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((R + kWarps * 2 - 1) / (kWarps * 2), H);
+  const __half* qp = static_cast<const __half*>(q_pool);
+  const __half* kp = static_cast<const __half*>(k_pool);
+  const __half* q2 = static_cast<const __half*>(q_second);
+  const __half* k2 = static_cast<const __half*>(k_second);
+  __half* prob = static_cast<__half*>(probability);
+  if (D == 64) {
+    if (cudaFuncSetAttribute(draft_jensen_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return ANEMOI_SM100_ELAUNCH;
+    draft_jensen_kernel<64><<<grid, kWarps * 32, smem, st>>>(qp, kp, q2, k2, R, prob);
+  } else {
+    if (cudaFuncSetAttribute(draft_jensen_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return ANEMOI_SM100_ELAUNCH;
+    draft_jensen_kernel<128><<<grid, kWarps * 32, smem, st>>>(qp, kp, q2, k2, R, prob);
+  }
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
 }

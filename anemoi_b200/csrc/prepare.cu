@@ -292,19 +292,22 @@ __device__ __forceinline__ void write_v_nvfp4(uint8_t* codes, uint8_t* sf, const
 }
 
 template <int D>
+// `second`: the extra pool holds the second moments (mean of the squares, one FMA per row in
+// row order; padding rows are zero) instead of the maxima - the diag-Jensen draft map's input.
 __device__ __forceinline__ void write_pools(const __half* tile, int rows, int count, __half* mean,
-                                            __half* maxp) {
+                                            __half* maxp, bool second) {
   if (threadIdx.x < D) {
     const int c = threadIdx.x;
-    float sum = 0.0f, mx = -INFINITY;
+    float sum = 0.0f, mx = -INFINITY, sq = 0.0f;
 #pragma unroll 8
     for (int r = 0; r < rows; ++r) {
       const float x = __half2float(tile[r * (D + kPad) + c]);
       sum = __fadd_rn(sum, x);
+      sq = __fmaf_rn(x, x, sq);
       if (r < count) mx = fmaxf(mx, x);
     }
     mean[c] = __float2half_rn(__fdiv_rn(sum, (float)count));
-    if (maxp != nullptr) maxp[c] = __float2half_rn(mx);
+    if (maxp != nullptr) maxp[c] = __float2half_rn(second ? __fdiv_rn(sq, (float)count) : mx);
   }
 }
 
@@ -339,7 +342,7 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
       __half* mx = p.s.has_maxpool
                        ? static_cast<__half*>(p.o.q_max_pool) + ((int64_t)head * R + t) * D
                        : nullptr;
-      write_pools<D>(tile, QB, valid, mean, mx);
+      write_pools<D>(tile, QB, valid, mean, mx, p.s.has_maxpool == 2);
       if (p.s.has_fp16) {
         write_fp16_tile<D>(static_cast<uint8_t*>(p.o.q_fp16) +
                                ((int64_t)head * R + t) * rec::q_fp16_bytes(QB, D),
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(kThreads) prepare_kernel(PrepParams p) {
     __half* mx = p.s.has_maxpool
                      ? static_cast<__half*>(p.o.k_max_pool) + ((int64_t)head * R + b) * D
                      : nullptr;
-    write_pools<D>(tile, QB, valid, mean, mx);
+    write_pools<D>(tile, QB, valid, mean, mx, p.s.has_maxpool == 2);
   }
   for (int g = 0; g < nst; ++g) {
     if (p.s.has_fp16) {

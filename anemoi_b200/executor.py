@@ -147,10 +147,17 @@ def sm100_ragged_attention(
     nvfp4_scales: tuple[float, float, float] = (1.0, 1.0, 1.0),
     return_parts: bool = False,
     profile_nvtx: bool = False,
+    diag_jensen: bool = False,
 ):
-    """Per-frame ragged Q64/Q128 routing and mixed-precision attention on sm_100a."""
-    if type(profile_nvtx) is not bool:
-        raise TypeError("profile_nvtx must be a bool")
+    """Per-frame ragged Q64/Q128 routing and mixed-precision attention on sm_100a.
+
+    ``diag_jensen`` selects the reference's experimental diag-Jensen draft map (second moments of
+    the blocks added to the pooled logits, anemoi/layers/attention/mpa/executor.py:1105-1126); as
+    there, it cannot be combined with the max-pool blend."""
+    if type(profile_nvtx) is not bool or type(diag_jensen) is not bool:
+        raise TypeError("profile_nvtx and diag_jensen must be bool")
+    if diag_jensen and maxpool_weight != 0.0:
+        raise ValueError("maxpool_weight cannot be combined with diag_jensen")
     with _Range("anemoi.complete", profile_nvtx or _PROFILE_NVTX):
         return _ragged_attention(
             q_bshd, k_bshd, v_bshd, prefix_tokens=prefix_tokens, sparsity_ratio=sparsity_ratio,
@@ -159,13 +166,13 @@ def sm100_ragged_attention(
             query_block_size=query_block_size, prefix_kv_precision=prefix_kv_precision,
             prefix_query_precision=prefix_query_precision, maxpool_weight=maxpool_weight,
             nvfp4_scales=nvfp4_scales, return_parts=return_parts,
-            nvtx=profile_nvtx or _PROFILE_NVTX)
+            nvtx=profile_nvtx or _PROFILE_NVTX, diag_jensen=diag_jensen)
 
 
 def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, retained_nvfp4_ratio,
                       retained_int8_ratio, retained_fp16_ratio, video_shape, layer, query_block_size,
                       prefix_kv_precision, prefix_query_precision, maxpool_weight, nvfp4_scales,
-                      return_parts, nvtx):
+                      return_parts, nvtx, diag_jensen=False):
     if q_bshd.shape != k_bshd.shape or q_bshd.shape != v_bshd.shape:
         raise ValueError("Q/K/V must share [1,S,H,D], D in {64,128}")
     if (
@@ -227,7 +234,7 @@ def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, 
     blocks = layout.video_blocks
     shape = make_shape(q_bshd, prefix_tokens=prefix_tokens, video_blocks=blocks,
                        query_block_size=query_block_size, active=active,
-                       native_prefix=native_prefix, has_maxpool=maxpool_weight != 0.0,
+                       native_prefix=native_prefix, has_maxpool=2 if diag_jensen else maxpool_weight != 0.0,
                        nvfp4_scales=nvfp4_scales)
     store = native.allocate_operands(shape, device)
     with _Stage("prepare"), _Range("anemoi.peripheral.prepare", nvtx):
@@ -248,7 +255,8 @@ def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, 
 
     with _Range("anemoi.peripheral.draft_route_materialize", nvtx):
         with _Stage("draft"):
-            prob = native.draft_probability(shape, store, float(maxpool_weight))
+            prob = (native.draft_probability_jensen(shape, store) if diag_jensen
+                    else native.draft_probability(shape, store, float(maxpool_weight)))
         n16, n8, n4 = route_counts(blocks * blocks, sparsity_ratio=float(sparsity_ratio),
                                    nvfp4_ratio=float(retained_nvfp4_ratio),
                                    int8_ratio=float(retained_int8_ratio),

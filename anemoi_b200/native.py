@@ -86,6 +86,7 @@ def library() -> C.CDLL:
         "anemoi_sm100_operand_bytes": (I64, [SP, C.c_int]),
         "anemoi_sm100_prepare": (C.c_int, [SP, P, P, P, C.POINTER(I64), P, P, OP, P]),
         "anemoi_sm100_draft_probability": (C.c_int, [SP, P, P, P, P, F, P, P]),
+        "anemoi_sm100_draft_probability_jensen": (C.c_int, [SP, P, P, P, P, P, P]),
         "anemoi_sm100_route_scratch_bytes": (I64, [SP]),
         "anemoi_sm100_route_list_capacity": (I64, [SP, I64, I64, I64, C.c_int]),
         "anemoi_sm100_route": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, I64, P, P, P, I64, P]),
@@ -131,7 +132,7 @@ def library() -> C.CDLL:
 
 EXPORTED = (
     "anemoi_sm100_arch", "anemoi_sm100_operand_bytes", "anemoi_sm100_prepare",
-    "anemoi_sm100_draft_probability", "anemoi_sm100_route_scratch_bytes",
+    "anemoi_sm100_draft_probability", "anemoi_sm100_draft_probability_jensen", "anemoi_sm100_route_scratch_bytes",
     "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_attention_pairs", "anemoi_sm100_pair_lists",
@@ -228,6 +229,21 @@ def draft_probability(shape: Shape, store: OperandStore, maxpool_weight: float) 
         C.byref(shape), _ptr(b["q_pool"]), _ptr(b["k_pool"]), _ptr(b["q_max_pool"]),
         _ptr(b["k_max_pool"]), float(maxpool_weight), _ptr(prob), _stream(prob.device)),
         "anemoi_sm100_draft_probability")
+    return prob
+
+
+def draft_probability_jensen(shape: Shape, store: OperandStore) -> torch.Tensor:
+    """The diag-Jensen draft map; the operands' extra pool slots hold the second moments
+    (``shape.has_maxpool == 2``)."""
+    if shape.has_maxpool != 2:
+        raise ValueError("the operands were not prepared with second moments")
+    b = store.buffers
+    r = shape.video_blocks
+    prob = torch.empty((shape.heads, r, r), dtype=torch.float16, device=b["q_pool"].device)
+    _count("draft", 1)
+    _check(library().anemoi_sm100_draft_probability_jensen(
+        C.byref(shape), _ptr(b["q_pool"]), _ptr(b["k_pool"]), _ptr(b["q_max_pool"]), _ptr(b["k_max_pool"]),
+        _ptr(prob), _stream(prob.device)), "anemoi_sm100_draft_probability_jensen")
     return prob
 
 

@@ -86,7 +86,10 @@ def synth_qkv(w, heads: int, device, seed: int, rows: slice | None = None, dtype
 
 
 class ClockSampler:
-    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    """Samples the GPU's SM clock and throttle reasons while the timed region runs: NVML queries
+    from a thread of this process every 10 ms (read-only; a sample is also taken on entry and on
+    exit, so that a region of a few milliseconds still has some), or `nvidia-smi -lms` when the
+    NVML binding is missing."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -96,8 +99,44 @@ class ClockSampler:
         self.index = index
         self.rows: list[list[str]] = []
         self.proc = None
+        self.nvml = None
+        self.handle = None
+        self.stop = threading.Event()
+
+    def _open_nvml(self) -> bool:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml = pynvml
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _sample_nvml(self) -> None:
+        n = self.nvml
+        try:
+            sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+            mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+            mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
+                n, "nvmlDeviceGetCurrentClocksEventReasons") else n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        except Exception:
+            return
+        bits = (0x8, 0x40, 0x20, 0x4)    # hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        self.rows.append([str(sm), str(mx)] + ["Active" if mask & b else "Not Active" for b in bits])
 
     def __enter__(self):
+        if self._open_nvml():
+            self._sample_nvml()
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
@@ -109,12 +148,24 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def _poll(self):
+        while not self.stop.wait(0.01):
+            self._sample_nvml()
+
     def _pump(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *exc):
-        if self.proc is not None:
+        if self.nvml is not None:
+            self.stop.set()
+            self.thread.join(timeout=2)
+            self._sample_nvml()
+            try:
+                self.nvml.nvmlShutdown()
+            except Exception:
+                pass
+        elif self.proc is not None:
             self.proc.terminate()
             self.proc.wait(timeout=5)
             self.thread.join(timeout=2)
@@ -132,7 +183,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def measured_peaks() -> tuple[dict, str]:

@@ -40,7 +40,7 @@ typedef struct anemoi_sm100_shape {
   int32_t has_int8;
   int32_t has_fp16;
   int32_t has_prefix_query_int8; /* prefix queries run through the INT8 cell */
-  int32_t has_maxpool;
+  int32_t has_maxpool;          /* 1: max pools in the extra pool slots; 2: second moments (diag-Jensen) */
   int32_t input_is_bf16;    /* raw Q/K/V dtype: 1 bf16, 0 fp16 */
   float q_global_scale;     /* NVFP4 tensor-level scales (NVFP4Calibration) */
   float k_global_scale;
@@ -105,6 +105,16 @@ int anemoi_sm100_draft_probability(const anemoi_sm100_shape* shape, const void* 
                                    const void* k_pool, const void* q_max_pool,
                                    const void* k_max_pool, float maxpool_weight,
                                    void* probability, void* stream);
+
+/* The diag-Jensen draft map, an experimental routing proxy of the reference
+ * (mpa/routing.py:87-103, enabled by `diag_jensen` in mpa/executor.py:1105-1126; never combined
+ * with the max-pool blend): logits q.k/sqrt(D) + 0.5 * max((q2.k2 - (q*q).(k*k)) / D, 0) in fp32,
+ * row softmax, fp16 [H][R][R].  `q_second`, `k_second` [H][R][D] fp16 are the per-channel second
+ * moments of the blocks; anemoi_sm100_prepare writes them into the max-pool slots of the operands
+ * when shape.has_maxpool == 2.  The reference computes this map with torch matmuls. */
+int anemoi_sm100_draft_probability_jensen(const anemoi_sm100_shape* shape, const void* q_pool,
+                                          const void* k_pool, const void* q_second,
+                                          const void* k_second, void* probability, void* stream);
 
 /* Bytes of scratch anemoi_sm100_route needs for `shape`. */
 int64_t anemoi_sm100_route_scratch_bytes(const anemoi_sm100_shape* shape);

@@ -34,7 +34,7 @@ def resolve(nvfp4_ratio, int8_ratio, fp16_ratio, prefix_tokens, prefix_kv_precis
 
 def head_attention(q, k, v, geo: P.Geometry, *, sparsity, ratios, prefix_kv_precision="int8",
                    prefix_query_precision="int8", maxpool_weight=0.0,
-                   global_scales=(1.0, 1.0, 1.0), return_parts=False):
+                   global_scales=(1.0, 1.0, 1.0), return_parts=False, diag_jensen=False):
     """One head: ``q, k, v`` [S, D] -> fp16 [S, D] in raster order."""
     r4, r8, r16 = ratios
     d = q.shape[-1]
@@ -42,8 +42,11 @@ def head_attention(q, k, v, geo: P.Geometry, *, sparsity, ratios, prefix_kv_prec
     native_prefix = geo.prefix_tokens > 0 and prefix_query_precision == "int8" and "int8" in video
     ops = P.prepare_head(q, k, v, geo, has_nvfp4="nvfp4" in active, has_int8="int8" in active,
                          has_prefix_query_int8=native_prefix, has_maxpool=maxpool_weight != 0.0,
-                         global_scales=global_scales)
-    prob = R.draft_probability(ops.q_pool, ops.k_pool, ops.q_max, ops.k_max, maxpool_weight)
+                         global_scales=global_scales, second_moments=diag_jensen)
+    if diag_jensen:
+        prob = R.draft_probability_jensen(ops.q_pool, ops.k_pool, ops.q_max, ops.k_max)
+    else:
+        prob = R.draft_probability(ops.q_pool, ops.k_pool, ops.q_max, ops.k_max, maxpool_weight)
     rr = geo.video_blocks
     n16, n8, n4 = R.budgets(rr * rr, sparsity, r4, r8, r16)
     ids, low, mid, high = R.route(prob, n16, n8, n4)

@@ -119,6 +119,19 @@ def max_pool(video_rows: np.ndarray, geo: Geometry) -> np.ndarray:
     return np.where(valid, blocks, -np.inf).max(axis=1).astype(np.float16)
 
 
+def second_moment_pool(video_rows: np.ndarray, geo: Geometry) -> np.ndarray:
+    """fp16( (sum of squares over the block's slots in slot order, one FMA per slot, fp32) / real
+    count ): the per-channel second moments of the diag-Jensen draft map (reference:
+    anemoi/layers/attention/mpa/executor.py:1105-1124)."""
+    qb = geo.query_block
+    blocks = video_rows.reshape(-1, qb, video_rows.shape[-1]).astype(np.float64)
+    acc = np.zeros((blocks.shape[0], blocks.shape[2]), dtype=np.float32)
+    for s in range(qb):
+        # fma(x, x, acc): the square of an fp16 value is exact in fp64, one rounding to fp32
+        acc = (acc.astype(np.float64) + blocks[:, s] * blocks[:, s]).astype(np.float32)
+    return (acc / geo.counts.astype(np.float32)[:, None]).astype(np.float16)
+
+
 def int8_quantise(rows: np.ndarray, group_rows: int):
     """Symmetric INT8 per group of ``group_rows`` rows x all channels."""
     x = rows.astype(np.float32).reshape(-1, group_rows, rows.shape[-1])
@@ -160,7 +173,7 @@ class HeadOperands:
 
 def prepare_head(q, k, v, geo: Geometry, *, has_nvfp4: bool, has_int8: bool,
                  has_prefix_query_int8: bool, has_maxpool: bool,
-                 global_scales=(1.0, 1.0, 1.0)) -> HeadOperands:
+                 global_scales=(1.0, 1.0, 1.0), second_moments: bool = False) -> HeadOperands:
     """``q, k, v``: [S, D] of one head (any float dtype; narrowed to fp16 first)."""
     q16, k16, v16 = (F.narrow_to_fp16(t) for t in (q, k, v))
     qp = pack_rows(q16, geo, with_prefix=False)
@@ -173,6 +186,9 @@ def prepare_head(q, k, v, geo: Geometry, *, has_nvfp4: bool, has_int8: bool,
         q_max=max_pool(qp, geo) if has_maxpool else None,
         k_max=max_pool(kp[cap:], geo) if has_maxpool else None,
     )
+    if second_moments:      # they travel in the max-pool slots (the two modes exclude each other)
+        ops.q_max = second_moment_pool(qp, geo)
+        ops.k_max = second_moment_pool(kp[cap:], geo)
     if has_int8:
         ops.q_i8, ops.q_i8_scale = int8_quantise(qp, geo.query_block)
         ops.k_i8, ops.k_i8_scale = int8_quantise(kp, 64)

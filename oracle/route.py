@@ -92,6 +92,34 @@ def draft_probability(q_pool, k_pool, q_max=None, k_max=None, maxpool_weight: fl
     return (a + b).astype(np.float32).astype(np.float16)
 
 
+def _dots32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """fp32 FMA chain over the channels in ascending order (a, b fp32 [rows, D] / [cols, D])."""
+    acc = np.zeros((a.shape[0], b.shape[0]), dtype=np.float32)
+    for c in range(a.shape[1]):
+        acc = (acc.astype(np.float64) + a[:, c : c + 1].astype(np.float64) * b[None, :, c].astype(np.float64)
+               ).astype(np.float32)
+    return acc
+
+
+def draft_probability_jensen(q_pool, k_pool, q_second, k_second):
+    """Diag-Jensen draft map of one head (reference: anemoi/layers/attention/mpa/routing.py:87-103):
+    logits = q.k/sqrt(D) + 0.5 * max((q2.k2 - (q*q).(k*k)) / D, 0) in fp32 (not rounded to fp16),
+    row softmax, fp16.  Canonical arithmetic: every dot product is an FMA chain over ascending
+    channels (the inputs of the third one are the fp32 squares of the pools), the logit is
+    fma(0.5, max((v - w) * (1/D), 0), round(qk * (1/sqrt(D)))), the softmax the canonical one."""
+    d = q_pool.shape[-1]
+    q, k = q_pool.astype(np.float32), k_pool.astype(np.float32)
+    base = (_dots32(q, k) * np.float32(1.0 / math.sqrt(d))).astype(np.float32)
+    v = _dots32(q_second.astype(np.float32), k_second.astype(np.float32))
+    w = _dots32((q * q).astype(np.float32), (k * k).astype(np.float32))
+    t = np.maximum(((v - w).astype(np.float32) * np.float32(1.0 / d)).astype(np.float32), np.float32(0.0))
+    logits = (base.astype(np.float64) + 0.5 * t.astype(np.float64)).astype(np.float32)
+    m = logits.max(axis=1, keepdims=True)
+    e = exp_canonical((logits - m).astype(np.float32))
+    inv = (np.float32(1.0) / _row_sum32(e)).astype(np.float32)
+    return (e * inv[:, None]).astype(np.float32).astype(np.float16)
+
+
 def draft_probability_plain(q_pool, k_pool, q_max=None, k_max=None, maxpool_weight: float = 0.0):
     """Reference-style arithmetic: fp32 matmul, fp16 logits, fp32 softmax, fp16 result."""
     def soft(a, b):
