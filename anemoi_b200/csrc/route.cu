@@ -89,7 +89,10 @@ __device__ __forceinline__ long long block_exclusive(long long v, long long* war
 // ranked from the largest down) and B's offset inside that bin.  Two levels: sums of 32-bin
 // blocks (coalesced reads, one warp reduction each), a scan over the 1024 blocks, then one
 // warp per boundary resolves the bin inside the block that straddles it.
-__global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* thr, int64_t b0,
+// `sub` (optional): a second histogram that is subtracted bin by bin (the anchored variant ranks
+// the items that are not anchors).  The results go to thr[head * thr_stride + thr_first ..].
+__global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, const int* sub, int* thr,
+                                                         int thr_stride, int thr_first, int64_t b0,
                                                          int64_t b1, int64_t b2) {
   __shared__ long long warp_sum[32];
   __shared__ int block_sum[1024];
@@ -97,11 +100,13 @@ __global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* t
   __shared__ long long hit_off[3];
   const int head = blockIdx.x;
   const int* h = hist + (int64_t)head * kBins;
+  const int* hs = sub ? sub + (int64_t)head * kBins : nullptr;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int mine = 0;
 #pragma unroll 4
   for (int i = 0; i < 32; ++i) {
-    const int sum = __reduce_add_sync(0xffffffffu, h[(warp * 32 + i) * 32 + lane]);
+    const int bin = (warp * 32 + i) * 32 + lane;
+    const int sum = __reduce_add_sync(0xffffffffu, h[bin] - (hs ? hs[bin] : 0));
     if (lane == i) mine = sum;
   }
   block_sum[threadIdx.x] = mine;
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* t
     const int hb = hit_block[warp];
     if (hb >= 0) {
       const int bin = hb * 32 + 31 - lane;  // descending inside the block
-      const int n = h[bin];
+      const int n = h[bin] - (hs ? hs[bin] : 0);
       int incl = n;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -140,8 +145,8 @@ __global__ void __launch_bounds__(1024) threshold_kernel(const int* hist, int* t
       quota = __shfl_sync(0xffffffffu, (int)(off - (incl - n)), src);
     }
     if (lane == 0) {
-      thr[head * 8 + 2 * warp] = key;
-      thr[head * 8 + 2 * warp + 1] = quota;
+      thr[head * thr_stride + thr_first + 2 * warp] = key;
+      thr[head * thr_stride + thr_first + 2 * warp + 1] = quota;
     }
   }
 }
@@ -303,6 +308,220 @@ __global__ void __launch_bounds__(kRowWarps * 32) emit_kernel(
   }
 }
 
+// ---- routing with anchors (an experimental variant of the reference,
+// anemoi/layers/attention/mpa/routing.py:190-203, sm120/h3_route_precision.cu:160-220) -------------
+// Anchor pairs (a fixed [R][R] mask shared by the heads: the same-frame neighbours of a block) that
+// the ranking dropped are forced into the lowest active precision, and as many of the
+// lowest-ranked pairs of that precision that are not anchors are dropped instead.  Restated as
+// selection: every anchor is kept (at the precision of its rank, or the lowest one), and of
+// the other pairs exactly the retained - anchor_count best ranked are kept, at the precision
+// of their rank among all pairs.  So a fourth boundary is taken in the ranking of the pairs
+// that are not anchors (their histogram is the full one minus the anchors').  A pair's
+// precision then depends on the anchor mask, and the per-row counts are taken by a pass of
+// their own before the offsets are scanned.
+constexpr int kAnchorStat = 4;  // ints per row: items equal to straddling key 0,1,2; non-anchors equal to key 3
+
+__global__ void __launch_bounds__(256) anchor_hist_kernel(const unsigned short* prob, int64_t items,
+                                                          const int32_t* anchor_ids, int count,
+                                                          int* hist_anchor) {
+  const int i = blockIdx.x * 256 + threadIdx.x, head = blockIdx.y;
+  if (i >= count) return;
+  const int key = __ldg(prob + (int64_t)head * items + anchor_ids[i]) & 0x7fff;
+  atomicAdd(hist_anchor + (int64_t)head * kBins + key, 1);
+}
+
+struct AnchorRow {
+  int key_b[4], quota_b[4], run[4];
+};
+
+__device__ __forceinline__ AnchorRow anchor_row(const int* thr, const int* stat, int head, int R,
+                                                int row) {
+  AnchorRow a;
+  const int* st = stat + ((int64_t)head * R + row) * kAnchorStat;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    a.key_b[b] = thr[head * 16 + (b < 3 ? 2 * b : 8)];
+    a.quota_b[b] = thr[head * 16 + (b < 3 ? 2 * b + 1 : 9)];
+    a.run[b] = st[b];
+  }
+  return a;
+}
+
+// Precision code of the lane's column (0 = dropped); advances the row's tie counters.
+__device__ __forceinline__ int anchor_code(AnchorRow& a, int key, bool in, bool anchor, unsigned lower,
+                                           int lowest_code) {
+  bool below[3];
+#pragma unroll
+  for (int b = 0; b < 3; ++b) {
+    const bool tie = in && key == a.key_b[b];
+    const unsigned ties = __ballot_sync(0xffffffffu, tie);
+    below[b] = key > a.key_b[b] || (tie && a.run[b] + __popc(ties & lower) < a.quota_b[b]);
+    a.run[b] += __popc(ties);
+  }
+  const bool tie = in && !anchor && key == a.key_b[3];
+  const unsigned ties = __ballot_sync(0xffffffffu, tie);
+  const bool kept = key > a.key_b[3] || (tie && a.run[3] + __popc(ties & lower) < a.quota_b[3]);
+  a.run[3] += __popc(ties);
+  const int ranked = below[0] ? 3 : (below[1] ? 2 : (below[2] ? 1 : 0));
+  if (!in) return 0;
+  if (anchor) return ranked ? ranked : lowest_code;
+  return kept ? ranked : 0;
+}
+
+// One warp per row: items equal to each straddling key (the fourth among the non-anchors only).
+__global__ void __launch_bounds__(kRowWarps * 32) anchor_rowstat_kernel(const unsigned short* prob,
+                                                                        const uint8_t* anchors, int R,
+                                                                        const int* thr, int* stat) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (row >= R) return;
+  const int lane = threadIdx.x & 31;
+  const int k0 = thr[head * 16], k1 = thr[head * 16 + 2], k2 = thr[head * 16 + 4],
+            k3 = thr[head * 16 + 8];
+  const unsigned short* src = prob + ((int64_t)head * R + row) * R;
+  const uint8_t* an = anchors + (int64_t)row * R;
+  int e0 = 0, e1 = 0, e2 = 0, e3 = 0;
+  for (int j = lane; j < R; j += 32) {
+    const int key = __ldg(src + j) & 0x7fff;
+    e0 += key == k0;
+    e1 += key == k1;
+    e2 += key == k2;
+    e3 += key == k3 && !an[j];
+  }
+  e0 = __reduce_add_sync(0xffffffffu, e0);
+  e1 = __reduce_add_sync(0xffffffffu, e1);
+  e2 = __reduce_add_sync(0xffffffffu, e2);
+  e3 = __reduce_add_sync(0xffffffffu, e3);
+  if (lane < 4)
+    stat[((int64_t)head * R + row) * kAnchorStat + lane] = lane == 0 ? e0 : lane == 1 ? e1 : lane == 2 ? e2 : e3;
+}
+
+// One CTA per head: the equal-counts become exclusive prefixes over the rows.
+__global__ void __launch_bounds__(1024) anchor_tiescan_kernel(int R, int* stat) {
+  __shared__ long long warp_sum[32];
+  const int head = blockIdx.x;
+  long long carry[4] = {0, 0, 0, 0};
+  for (int r0 = 0; r0 < R; r0 += 1024) {
+    const int row = r0 + threadIdx.x;
+    const bool in = row < R;
+    int* st = stat + ((int64_t)head * R + row) * kAnchorStat;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int eq = in ? st[b] : 0;
+      long long all;
+      const long long pre = carry[b] + block_exclusive(eq, warp_sum, all);
+      carry[b] += all;
+      if (in) st[b] = (int)pre;
+    }
+  }
+}
+
+// One warp per row: pairs per precision (entries 0..2 of the row's counts, in logical blocks).
+__global__ void __launch_bounds__(kRowWarps * 32) anchor_count_kernel(const unsigned short* prob,
+                                                                      const uint8_t* anchors, int R,
+                                                                      const int* thr, const int* stat,
+                                                                      int lowest_code, int32_t* row_counts) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (row >= R) return;
+  const int lane = threadIdx.x & 31;
+  const unsigned lower = (1u << lane) - 1u;
+  AnchorRow a = anchor_row(thr, stat, head, R, row);
+  const unsigned short* src = prob + ((int64_t)head * R + row) * R;
+  const uint8_t* an = anchors + (int64_t)row * R;
+  int n[3] = {0, 0, 0};
+  for (int j0 = 0; j0 < R; j0 += 32) {
+    const int j = j0 + lane;
+    const bool in = j < R;
+    const int key = in ? (__ldg(src + j) & 0x7fff) : -2;
+    const int c = anchor_code(a, key, in, in && an[j] != 0, lower, lowest_code);
+#pragma unroll
+    for (int k = 1; k <= 3; ++k) n[k - 1] += __popc(__ballot_sync(0xffffffffu, c == k));
+  }
+  if (lane < 3) row_counts[((int64_t)head * R + row) * 4 + lane] = n[lane];
+}
+
+// One CTA per head: stages per phase from the pair counts, list offsets in row order, launch order.
+__global__ void __launch_bounds__(1024) anchor_offsets_kernel(int R, int factor, int prefix_stages,
+                                                              int prefix_phase, int32_t* row_offset,
+                                                              int32_t* row_counts) {
+  __shared__ long long warp_sum[32];
+  __shared__ int total_s[kOrderMaxBlocks];
+  const int head = blockIdx.x;
+  const int p = prefix_phase >= 0 ? prefix_stages : 0;
+  long long carry = 0;
+  for (int r0 = 0; r0 < R; r0 += 1024) {
+    const int row = r0 + threadIdx.x;
+    const bool in = row < R;
+    int32_t* rc = row_counts + ((int64_t)head * R + row) * 4;
+    int n[3] = {0, 0, 0};
+    if (in)
+      for (int c = 0; c < 3; ++c) n[c] = rc[c] * factor + (prefix_phase == c ? p : 0);
+    const int total = n[0] + n[1] + n[2];
+    long long all;
+    const long long off = carry + block_exclusive(total, warp_sum, all);
+    carry += all;
+    if (in) {
+      row_offset[(int64_t)head * R + row] = (int32_t)off;
+      rc[0] = n[0];
+      rc[1] = n[1];
+      rc[2] = n[2];
+      rc[3] = 0;
+      if (row < kOrderMaxBlocks) total_s[row] = total;
+    }
+  }
+  if (R > kOrderMaxBlocks) return;
+  __syncthreads();
+  int32_t* rc = row_counts + (int64_t)head * R * 4;
+  for (int i = threadIdx.x; i < R; i += 1024) {
+    const int mine = total_s[i];
+    int rank = 0;
+    for (int j = 0; j < R; ++j) rank += (total_s[j] > mine) || (total_s[j] == mine && j < i);
+    rc[rank * 4 + 3] = i + 1;
+  }
+}
+
+// One warp per row writes the row's list (as emit_kernel, with the anchored codes).
+__global__ void __launch_bounds__(kRowWarps * 32) anchor_emit_kernel(
+    const unsigned short* prob, const uint8_t* anchors, int R, const int* thr, const int* stat,
+    int lowest_code, int factor, int prefix_stages, int prefix_phase, int64_t capacity,
+    const int32_t* row_offset, const int32_t* row_counts, int32_t* stage_ids) {
+  const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5), head = blockIdx.y;
+  if (row >= R) return;
+  const int lane = threadIdx.x & 31;
+  const unsigned lower = (1u << lane) - 1u;
+  AnchorRow a = anchor_row(thr, stat, head, R, row);
+  const int32_t* rc = row_counts + ((int64_t)head * R + row) * 4;
+  const int n0 = rc[0], n1 = rc[1], n2 = rc[2];
+  const int total = n0 + n1 + n2;
+  if (total == 0) return;
+  const int64_t base = row_offset[(int64_t)head * R + row];
+  if (base + total > capacity) return;
+  int32_t* list = stage_ids + (int64_t)head * capacity + base;
+  const int p = prefix_phase >= 0 ? prefix_stages : 0;
+  int at[3] = {prefix_phase == 0 ? p : 0, n0 + (prefix_phase == 1 ? p : 0),
+               n0 + n1 + (prefix_phase == 2 ? p : 0)};
+  if (prefix_phase >= 0) {
+    const int seg = prefix_phase == 0 ? 0 : (prefix_phase == 1 ? n0 : n0 + n1);
+    for (int s = lane; s < p; s += 32) list[seg + s] = s;
+  }
+  const unsigned short* src = prob + ((int64_t)head * R + row) * R;
+  const uint8_t* an = anchors + (int64_t)row * R;
+  for (int j0 = 0; j0 < R; j0 += 32) {
+    const int j = j0 + lane;
+    const bool in = j < R;
+    const int key = in ? (__ldg(src + j) & 0x7fff) : -2;
+    const int c = anchor_code(a, key, in, in && an[j] != 0, lower, lowest_code);
+#pragma unroll
+    for (int k = 1; k <= 3; ++k) {
+      const unsigned members = __ballot_sync(0xffffffffu, c == k);
+      if (c == k) {
+        int32_t* dst = list + at[k - 1] + __popc(members & lower) * factor;
+        for (int e = 0; e < factor; ++e) dst[e] = prefix_stages + j * factor + e;
+      }
+      at[k - 1] += __popc(members) * factor;
+    }
+  }
+}
+
 // Q64 query blocks 2t and 2t+1 of a head run as one CTA of the attention kernel (rows 0-63 and
 // 64-127 of the 128-row MMA shape).  That CTA walks, phase by phase, the union of the two
 // blocks' lists; bits 30 and 31 of an entry say which of the two blocks the stage belongs to.
@@ -365,6 +584,64 @@ __global__ void __launch_bounds__(1024) pair_order_kernel(int pairs, int32_t* pa
 }
 
 }  // namespace
+
+extern "C" int64_t anemoi_sm100_route_anchored_scratch_bytes(const anemoi_sm100_shape* shape) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK) return ANEMOI_SM100_EINVAL;
+  return (int64_t)shape->heads * (2 * kBins + 16 + kAnchorStat * (int64_t)shape->video_blocks) * 4;
+}
+
+extern "C" int anemoi_sm100_route_anchored(const anemoi_sm100_shape* shape, const void* probability,
+                                           int64_t n16, int64_t n8, int64_t n4, int prefix_phase,
+                                           const uint8_t* anchors, const int32_t* anchor_ids,
+                                           int32_t anchor_count, void* scratch, int64_t scratch_bytes,
+                                           int32_t* row_offset, int32_t* row_counts,
+                                           int32_t* stage_ids, int64_t list_capacity, void* stream) {
+  if (rec::validate_shape(shape) != ANEMOI_SM100_OK || !probability || !scratch || !row_offset ||
+      !row_counts || !stage_ids || !anchors || !anchor_ids || anchor_count <= 0)
+    return ANEMOI_SM100_EINVAL;
+  const int H = shape->heads, R = shape->video_blocks;
+  const int64_t items = (int64_t)R * R, retained = n16 + n8 + n4;
+  if (n16 < 0 || n8 < 0 || n4 < 0 || retained > items || retained <= 0) return ANEMOI_SM100_EINVAL;
+  // as the reference: the anchors must fit into the lowest active precision
+  const int64_t lowest = n4 ? n4 : (n8 ? n8 : n16);
+  if (anchor_count > lowest) return ANEMOI_SM100_EINVAL;
+  if (prefix_phase < -1 || prefix_phase > 2) return ANEMOI_SM100_EINVAL;
+  if (prefix_phase >= 0 && shape->prefix_tokens == 0) prefix_phase = -1;
+  if (scratch_bytes < anemoi_sm100_route_anchored_scratch_bytes(shape)) return ANEMOI_SM100_EINVAL;
+  if (list_capacity < anemoi_sm100_route_list_capacity(shape, n16, n8, n4, prefix_phase))
+    return ANEMOI_SM100_EINVAL;
+  if (R > 65535 || items * H >= (1ll << 40)) return ANEMOI_SM100_ELIMIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* hist = static_cast<int*>(scratch);
+  int* hist_anchor = hist + (int64_t)H * kBins;
+  int* thr = hist_anchor + (int64_t)H * kBins;
+  int* stat = thr + (int64_t)H * 16;
+  if (cudaMemsetAsync(hist, 0, (size_t)H * kBins * 8, st) != cudaSuccess) return ANEMOI_SM100_ELAUNCH;
+  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBins * 4) !=
+      cudaSuccess)
+    return ANEMOI_SM100_ELAUNCH;
+  const unsigned short* prob = static_cast<const unsigned short*>(probability);
+  const int chunks = (int)max((int64_t)1, min(min((int64_t)16, items / 8192), (int64_t)((296 + H / 2) / H)));
+  const int factor = shape->query_block / 64, prefix_stages = rec::prefix_stages(*shape);
+  const int lowest_code = n4 ? 1 : (n8 ? 2 : 3);
+  const dim3 rows((R + kRowWarps - 1) / kRowWarps, H);
+  hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, hist);
+  anchor_hist_kernel<<<dim3((anchor_count + 255) / 256, H), 256, 0, st>>>(prob, items, anchor_ids,
+                                                                           anchor_count, hist_anchor);
+  threshold_kernel<<<H, 1024, 0, st>>>(hist, nullptr, thr, 16, 0, n16, n16 + n8, retained);
+  const int64_t others = retained - anchor_count;  // pairs kept that are not anchors
+  threshold_kernel<<<H, 1024, 0, st>>>(hist, hist_anchor, thr, 16, 8, others, others, others);
+  anchor_rowstat_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, anchors, R, thr, stat);
+  anchor_tiescan_kernel<<<H, 1024, 0, st>>>(R, stat);
+  anchor_count_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, anchors, R, thr, stat, lowest_code,
+                                                       row_counts);
+  anchor_offsets_kernel<<<H, 1024, 0, st>>>(R, factor, prefix_stages, prefix_phase, row_offset,
+                                            row_counts);
+  anchor_emit_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, anchors, R, thr, stat, lowest_code, factor,
+                                                      prefix_stages, prefix_phase, list_capacity,
+                                                      row_offset, row_counts, stage_ids);
+  return cudaGetLastError() == cudaSuccess ? ANEMOI_SM100_OK : ANEMOI_SM100_ELAUNCH;
+}
 
 extern "C" int anemoi_sm100_pair_lists(const anemoi_sm100_shape* shape, const int32_t* row_offset,
                                        const int32_t* row_counts, const int32_t* stage_ids,
@@ -433,7 +710,7 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
   const int factor = shape->query_block / 64, prefix_stages = rec::prefix_stages(*shape);
   const dim3 rows((R + kRowWarps - 1) / kRowWarps, H);
   hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, sc.hist);
-  threshold_kernel<<<H, 1024, 0, st>>>(sc.hist, sc.thr, n16, n16 + n8, n16 + n8 + n4);
+  threshold_kernel<<<H, 1024, 0, st>>>(sc.hist, nullptr, sc.thr, 8, 0, n16, n16 + n8, n16 + n8 + n4);
   rowstat_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, R, sc.thr, sc.stat);
   headscan_kernel<<<H, 1024, 0, st>>>(R, sc.thr, sc.stat, factor, prefix_stages, prefix_phase,
                                       row_offset, row_counts);

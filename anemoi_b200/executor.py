@@ -148,14 +148,19 @@ def sm100_ragged_attention(
     return_parts: bool = False,
     profile_nvtx: bool = False,
     diag_jensen: bool = False,
+    enable_anchors: bool = False,
 ):
     """Per-frame ragged Q64/Q128 routing and mixed-precision attention on sm_100a.
+
+    ``enable_anchors`` selects the reference's experimental anchored routing: every pair of
+    same-frame neighbouring blocks is kept, at the lowest active precision if the ranking dropped
+    it (anemoi/layers/attention/mpa/executor.py:1151-1158, routing.py:190-203).
 
     ``diag_jensen`` selects the reference's experimental diag-Jensen draft map (second moments of
     the blocks added to the pooled logits, anemoi/layers/attention/mpa/executor.py:1105-1126); as
     there, it cannot be combined with the max-pool blend."""
-    if type(profile_nvtx) is not bool or type(diag_jensen) is not bool:
-        raise TypeError("profile_nvtx and diag_jensen must be bool")
+    if any(type(flag) is not bool for flag in (profile_nvtx, diag_jensen, enable_anchors)):
+        raise TypeError("profile_nvtx, diag_jensen and enable_anchors must be bool")
     if diag_jensen and maxpool_weight != 0.0:
         raise ValueError("maxpool_weight cannot be combined with diag_jensen")
     with _Range("anemoi.complete", profile_nvtx or _PROFILE_NVTX):
@@ -166,13 +171,13 @@ def sm100_ragged_attention(
             query_block_size=query_block_size, prefix_kv_precision=prefix_kv_precision,
             prefix_query_precision=prefix_query_precision, maxpool_weight=maxpool_weight,
             nvfp4_scales=nvfp4_scales, return_parts=return_parts,
-            nvtx=profile_nvtx or _PROFILE_NVTX, diag_jensen=diag_jensen)
+            nvtx=profile_nvtx or _PROFILE_NVTX, diag_jensen=diag_jensen, enable_anchors=enable_anchors)
 
 
 def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, retained_nvfp4_ratio,
                       retained_int8_ratio, retained_fp16_ratio, video_shape, layer, query_block_size,
                       prefix_kv_precision, prefix_query_precision, maxpool_weight, nvfp4_scales,
-                      return_parts, nvtx, diag_jensen=False):
+                      return_parts, nvtx, diag_jensen=False, enable_anchors=False):
     if q_bshd.shape != k_bshd.shape or q_bshd.shape != v_bshd.shape:
         raise ValueError("Q/K/V must share [1,S,H,D], D in {64,128}")
     if (
@@ -230,7 +235,7 @@ def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, 
             )[0].contiguous()
 
     layout = materialize_ragged_2d_layout(device, frames=frames, height=height, width=width,
-                                          logical_block=query_block_size)
+                                          logical_block=query_block_size, enable_anchors=enable_anchors)
     blocks = layout.video_blocks
     shape = make_shape(q_bshd, prefix_tokens=prefix_tokens, video_blocks=blocks,
                        query_block_size=query_block_size, active=active,
@@ -263,7 +268,8 @@ def _ragged_attention(q_bshd, k_bshd, v_bshd, *, prefix_tokens, sparsity_ratio, 
                                    fp16_ratio=float(retained_fp16_ratio))
         phase_index = -1 if prefix_phase is None else PHASE_ORDER.index(prefix_phase)
         with _Stage("route"):
-            lists = native.route(shape, prob, n16, n8, n4, phase_index)
+            lists = (native.route_anchored(shape, prob, n16, n8, n4, phase_index, layout.anchors, layout.anchor_ids)
+                     if enable_anchors else native.route(shape, prob, n16, n8, n4, phase_index))
     with _Stage("attention"), _Range("anemoi.mpa_mainloop", nvtx):
         # Q64: two query blocks per CTA fill the 128-row MMA shape and walk the union of their lists
         pairs = native.pair_lists(shape, lists) if query_block_size == 64 and _PAIR_Q64 else None

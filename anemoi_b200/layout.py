@@ -31,6 +31,9 @@ class RaggedLayout:
     blocks_per_frame: int
     logical_block: int
     frames: int
+    anchors: torch.Tensor | None = None      # bool [R, R]: same-frame neighbours (enable_anchors)
+    anchor_ids: torch.Tensor | None = None   # int32: flat indices of the set entries, frame-major
+    anchor_count: int = 0
 
     @property
     def video_blocks(self) -> int:
@@ -39,8 +42,8 @@ class RaggedLayout:
 
 @lru_cache(maxsize=64)
 def _build(device_type: str, device_index: int | None, frames: int, height: int, width: int,
-           logical_block: int) -> RaggedLayout:
-    part = make_ragged_2d_partition(height, width, logical_block, include_adjacency=False)
+           logical_block: int, enable_anchors: bool = False) -> RaggedLayout:
+    part = make_ragged_2d_partition(height, width, logical_block, include_adjacency=enable_anchors)
     per_frame = part.block_count
     frame_tokens = height * width
     local = torch.zeros((per_frame, logical_block), dtype=torch.int64)
@@ -57,6 +60,21 @@ def _build(device_type: str, device_index: int | None, frames: int, height: int,
     slots = torch.arange(indices.numel(), dtype=torch.int64)
     inverse[indices[slot_valid]] = slots[slot_valid]
     device = torch.device(device_type, device_index)
+    anchors = anchor_ids = None
+    anchor_count = 0
+    if enable_anchors:
+        # every (source, target) pair of neighbouring blocks of one frame, for every frame
+        # (reference: anemoi/layers/attention/mpa/layout.py:72-98)
+        total = frames * per_frame
+        pairs = torch.tensor([(a, b) for a, row in enumerate(part.adjacency) for b, near in enumerate(row) if near],
+                             dtype=torch.int64)
+        base = (torch.arange(frames, dtype=torch.int64) * per_frame).view(-1, 1)
+        ids = ((base + pairs[:, 0]) * total + base + pairs[:, 1]).reshape(-1)
+        mask = torch.zeros(total * total, dtype=torch.bool)
+        mask[ids] = True
+        anchors = mask.view(total, total).to(device).contiguous()
+        anchor_ids = ids.to(torch.int32).to(device).contiguous()
+        anchor_count = int(ids.numel())
     return RaggedLayout(
         indices=indices.to(torch.int32).to(device).contiguous(),
         slot_valid=slot_valid.to(device).contiguous(),
@@ -65,12 +83,18 @@ def _build(device_type: str, device_index: int | None, frames: int, height: int,
         blocks_per_frame=per_frame,
         logical_block=logical_block,
         frames=frames,
+        anchors=anchors,
+        anchor_ids=anchor_ids,
+        anchor_count=anchor_count,
     )
 
 
 def materialize_ragged_2d_layout(device, *, frames: int, height: int, width: int,
-                                 logical_block: int) -> RaggedLayout:
-    """Return the cached slot tables of a ``frames x height x width`` video."""
+                                 logical_block: int, enable_anchors: bool = False) -> RaggedLayout:
+    """Return the cached slot tables of a ``frames x height x width`` video (with the anchor mask
+    of the experimental anchored routing when ``enable_anchors``)."""
+    if type(enable_anchors) is not bool:
+        raise TypeError("enable_anchors must be a built-in bool")
     if logical_block not in (64, 128):
         raise ValueError("logical_block must be 64 or 128")
     if any(type(v) is not int or v <= 0 for v in (frames, height, width)):
@@ -79,7 +103,7 @@ def materialize_ragged_2d_layout(device, *, frames: int, height: int, width: int
     index = resolved.index
     if resolved.type == "cuda" and index is None:
         index = torch.cuda.current_device()
-    return _build(resolved.type, index, frames, height, width, logical_block)
+    return _build(resolved.type, index, frames, height, width, logical_block, enable_anchors)
 
 
 __all__ = ["RaggedLayout", "materialize_ragged_2d_layout"]

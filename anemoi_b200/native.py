@@ -91,6 +91,8 @@ def library() -> C.CDLL:
         "anemoi_sm100_route_list_capacity": (I64, [SP, I64, I64, I64, C.c_int]),
         "anemoi_sm100_route": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, I64, P, P, P, I64, P]),
         "anemoi_sm100_route_static_max_bytes": (I64, []),
+        "anemoi_sm100_route_anchored_scratch_bytes": (I64, [SP]),
+        "anemoi_sm100_route_anchored": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, I32, P, I64, P, P, P, I64, P]),
         "anemoi_sm100_route_static": (C.c_int, [SP, P, I64, I64, I64, C.c_int, P, P, P, I64, P]),
         "anemoi_sm100_attention": (C.c_int, [SP, OP, P, P, P, I64, P, P, P, P]),
         "anemoi_sm100_attention_pairs": (C.c_int, [SP, OP, P, P, P, P, I64, P, P, P, P]),
@@ -136,6 +138,7 @@ EXPORTED = (
     "anemoi_sm100_route_list_capacity", "anemoi_sm100_route", "anemoi_sm100_route_static",
     "anemoi_sm100_route_static_max_bytes", "anemoi_sm100_attention",
     "anemoi_sm100_attention_pairs", "anemoi_sm100_pair_lists",
+    "anemoi_sm100_route_anchored", "anemoi_sm100_route_anchored_scratch_bytes",
     "anemoi_sm100_prefix_attention", "anemoi_sm100_assemble", "anemoi_sm100_pack_qkv",
     "anemoi_sm100_merge_heads", "anemoi_sm100_pack_qkv_heads", "anemoi_sm100_merge_heads_into",
     "anemoi_sm100_tensor_peak", "anemoi_sm100_qknorm_rope", "anemoi_sm100_set_wait_limit_ns",
@@ -275,6 +278,39 @@ def route(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_p
                                   _ptr(scratch), scratch.numel(), _ptr(lists.row_offset),
                                   _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity,
                                   _stream(dev)), "anemoi_sm100_route")
+    return lists
+
+
+def route_anchored(shape: Shape, prob: torch.Tensor, n16: int, n8: int, n4: int, prefix_phase: int,
+                   anchors: torch.Tensor, anchor_ids: torch.Tensor) -> RouteLists:
+    """Routing with anchors: ``anchors`` ``(R, R)`` bool / uint8 mask shared by the heads,
+    ``anchor_ids`` its set flat indices (int32)."""
+    lib = library()
+    dev = prob.device
+    h, r = shape.heads, shape.video_blocks
+    if anchors.shape != (r, r) or anchors.dtype not in (torch.bool, torch.uint8) or anchor_ids.dtype != torch.int32:
+        raise ValueError("anchors must be an (R, R) bool mask and anchor_ids int32")
+    lowest = n4 or n8 or n16
+    if anchor_ids.numel() > lowest:
+        raise ValueError("anchor_count exceeds the configured lowest-precision budget")
+    scratch = torch.empty(int(lib.anemoi_sm100_route_anchored_scratch_bytes(C.byref(shape))), dtype=torch.uint8,
+                          device=dev)
+    if not shape.prefix_tokens:
+        prefix_phase = -1
+    cap = int(lib.anemoi_sm100_route_list_capacity(C.byref(shape), n16, n8, n4, prefix_phase))
+    lists = RouteLists(
+        row_offset=torch.empty((h, r), dtype=torch.int32, device=dev),
+        row_counts=torch.empty((h, r, 4), dtype=torch.int32, device=dev),
+        stage_ids=torch.empty((h, max(cap, 1)), dtype=torch.int32, device=dev),
+        capacity=max(cap, 1),
+    )
+    mask = anchors.contiguous().view(torch.uint8)
+    _count("route", 9)     # hist, anchor hist, 2 x threshold, rowstat, tie scan, count, offsets, emit
+    _check(lib.anemoi_sm100_route_anchored(
+        C.byref(shape), _ptr(prob), n16, n8, n4, prefix_phase, _ptr(mask), _ptr(anchor_ids),
+        int(anchor_ids.numel()), _ptr(scratch), scratch.numel(), _ptr(lists.row_offset),
+        _ptr(lists.row_counts), _ptr(lists.stage_ids), lists.capacity, _stream(dev)),
+        "anemoi_sm100_route_anchored")
     return lists
 
 

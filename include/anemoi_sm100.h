@@ -145,6 +145,22 @@ int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* probability,
                        int64_t scratch_bytes, int32_t* row_offset, int32_t* row_counts,
                        int32_t* stage_ids, int64_t list_capacity, void* stream);
 
+/* Routing with anchors, an experimental variant of the reference (mpa/routing.py:190-203,
+ * sm120/h3_route_precision.cu:160-220; off in the public path, enabled by `enable_anchors` in
+ * mpa/executor.py:1151-1158).  `anchors` is a [R][R] byte mask shared by the heads (the
+ * same-frame neighbours of every block, mpa/layout.py:69-98), `anchor_ids` its `anchor_count`
+ * set flat indices.  Anchor pairs the ranking dropped are forced into the lowest active
+ * precision and as many of the lowest-ranked other pairs of that precision are dropped
+ * instead; `anchor_count` must not exceed that precision's budget.  Same outputs as
+ * anemoi_sm100_route; scratch from anemoi_sm100_route_anchored_scratch_bytes. */
+int64_t anemoi_sm100_route_anchored_scratch_bytes(const anemoi_sm100_shape* shape);
+int anemoi_sm100_route_anchored(const anemoi_sm100_shape* shape, const void* probability,
+                                int64_t n16, int64_t n8, int64_t n4, int prefix_phase,
+                                const uint8_t* anchors, const int32_t* anchor_ids,
+                                int32_t anchor_count, void* scratch, int64_t scratch_bytes,
+                                int32_t* row_offset, int32_t* row_counts, int32_t* stage_ids,
+                                int64_t list_capacity, void* stream);
+
 /* Routing for callers that cannot provide scratch memory.  It has no counterpart in the
  * reference.  A host whose memory pool is fixed once it starts serving, or that must avoid
  * cudaMalloc / cudaFree on its request path (they synchronise the whole device), cannot

@@ -146,13 +146,18 @@ def budgets(items: int, sparsity: float, r4: float, r8: float, r16: float):
     return tuple(share)
 
 
-def route(prob16: np.ndarray, n16: int, n8: int, n4: int):
+def route(prob16: np.ndarray, n16: int, n8: int, n4: int, anchors: np.ndarray | None = None):
     """One head: [R, R] fp16 -> (ids [R, R] int32, low, middle, high counts [R] int32).
 
     Pairs are ranked by descending probability, ties by ascending flat index
     ``row * R + col``; ranks ``< n16`` are FP16 (code 3), the next ``n8`` INT8
     (code 2), the next ``n4`` NVFP4 (code 1).  Row lists hold the NVFP4 columns,
     then INT8, then FP16, each ascending; unused tail entries are 0.
+
+    ``anchors`` ([R, R] bool, the reference's experimental anchor variant,
+    anemoi/layers/attention/mpa/routing.py:190-203): anchor pairs the ranking dropped are
+    forced into the lowest active precision, and as many of the lowest-ranked pairs of that
+    precision that are not anchors are dropped instead.
     """
     r = prob16.shape[0]
     key = (prob16.astype(np.float16).view(np.uint16).astype(np.int64) & 0x7FFF).reshape(-1)
@@ -161,6 +166,16 @@ def route(prob16: np.ndarray, n16: int, n8: int, n4: int):
     code[order[:n16]] = 3
     code[order[n16 : n16 + n8]] = 2
     code[order[n16 + n8 : n16 + n8 + n4]] = 1
+    if anchors is not None:
+        lowest_code, lowest_count = (1, n4) if n4 else ((2, n8) if n8 else (3, n16))
+        retained = n16 + n8 + n4
+        mask = np.asarray(anchors, dtype=bool).reshape(-1)
+        missing = mask & (code == 0)
+        low_ids = order[retained - lowest_count : retained]
+        ordinary_reversed = ~mask[low_ids][::-1]
+        evict = (ordinary_reversed & (np.cumsum(ordinary_reversed) <= int(missing.sum())))[::-1]
+        code[low_ids[evict]] = 0
+        code[missing] = lowest_code
     code = code.reshape(r, r)
     ids = np.zeros((r, r), dtype=np.int32)
     counts = np.zeros((3, r), dtype=np.int32)
