@@ -109,9 +109,10 @@ class H3MPAConfig:
             raise ValueError("maxpool_weight must be finite and in [0, 1]")
         # knobs that have no sm_100a implementation stay off, as on the reference's public path
         if (float(self.fp8_ratio) != 0.0 or float(self.mxfp8_ratio) != 0.0 or self.draftmap_proxy != "mean"
-                or self.layer_draftmap_bands or self.diag_jensen or self.enable_anchors or self.smooth_k):
-            raise ValueError("fp8/mxfp8 phases, K-tail draft maps, diag_jensen, anchors and smooth_k "
-                             "are not available on sm_100a")
+                or self.layer_draftmap_bands or self.smooth_k):
+            raise ValueError("fp8/mxfp8 phases, K-tail draft maps and smooth_k are not available on sm_100a")
+        if self.diag_jensen and float(self.maxpool_weight) != 0.0:
+            raise ValueError("maxpool_weight cannot be combined with diag_jensen")
         ratios = (float(self.nvfp4_ratio), float(self.int8_ratio), float(self.fp16_ratio))
         if any(not math.isfinite(r) or r < 0.0 for r in ratios) or not math.isclose(sum(ratios), 1.0, abs_tol=1.0e-6):
             raise ValueError("native phases require nonnegative NVFP4/INT8/FP16 ratios summing to one")
@@ -298,6 +299,21 @@ class H3MPAAttention:
         if q.shape[0] != cfg.sequence_tokens:
             raise ValueError("packed sequence length does not match the H3 request")
         nvfp4, int8, _, fp16 = cfg.precision(layer)
+        if cfg.diag_jensen or cfg.enable_anchors:
+            # the experimental routing variants are not part of the public call; as in the
+            # reference's adapter (mpa_attention.py:584-600) the executor is called directly
+            from . import executor
+
+            calib = self.calibration(layer)
+            return executor.sm100_ragged_attention(
+                q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), prefix_tokens=cfg.prefix_tokens,
+                sparsity_ratio=cfg.sparsity(layer), retained_nvfp4_ratio=nvfp4, retained_int8_ratio=int8,
+                retained_fp16_ratio=fp16, video_shape=cfg.video_shape, layer=layer,
+                query_block_size=cfg.query_block_size, prefix_kv_precision=cfg.prefix_kv_precision,
+                prefix_query_precision=cfg.prefix_query_precision, maxpool_weight=float(cfg.maxpool_weight),
+                nvfp4_scales=(1.0, 1.0, 1.0) if calib is None else (calib.q_scale, calib.k_scale,
+                                                                     calib.v_scale),
+                diag_jensen=cfg.diag_jensen, enable_anchors=cfg.enable_anchors).squeeze(0)
         out = anemoi_attention(
             q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), layout=self._layout, layer=layer,
             sparse_config=SparseConfig(cfg.query_block_size, cfg.sparsity(layer), (), float(cfg.maxpool_weight)),
