@@ -20,7 +20,7 @@ class HostAttention:
     """Reusable state of the pipelined host-input call on one device: two sets of device
     input buffers for a head group and the two copy streams."""
 
-    def __init__(self, device, *, group_heads: int = 8):
+    def __init__(self, device, *, group_heads: int = 4):
         self.device = torch.device(device)
         self.group_heads = int(group_heads)
         if self.group_heads <= 0:

@@ -915,7 +915,7 @@ def main() -> None:
                     help="query blocks of attention timed per CPU sample (evenly spaced over the video)")
     ap.add_argument("--no-dense", action="store_true",
                     help="skip the dense bf16 library attention timed beside the sparse layer")
-    ap.add_argument("--e2e-group-heads", type=int, default=8,
+    ap.add_argument("--e2e-group-heads", type=int, default=4,
                     help="heads per group of the pipelined host-input call (end-to-end number)")
     ap.add_argument("--exchange", choices=("auto", "peer", "nccl"), default="auto",
                     help="N > 1: Ulysses exchange by stores into the peers' memory, by NCCL all-to-all, or "
