@@ -62,5 +62,37 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIBRARY
 
 
+TORCH_OPS = PACKAGE / "libanemoi_sm100_torch.so"
+
+
+def build_torch_ops(force: bool = False) -> Path:
+    """Compile ``csrc/torch_ops.cpp`` (host code: the ``torch.ops.anemoi_sm100`` registration over
+    the C ABI) with g++ against this interpreter's torch and link it to the C-ABI library."""
+    import torch
+    from torch.utils import cpp_extension
+
+    source = CSRC / "torch_ops.cpp"
+    header = PACKAGE.parent / "include" / "anemoi_sm100.h"
+    if (not force and TORCH_OPS.exists()
+            and TORCH_OPS.stat().st_mtime >= max(source.stat().st_mtime, header.stat().st_mtime, LIBRARY.stat().st_mtime)):
+        return TORCH_OPS
+    build()
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", str(source), "-o", str(TORCH_OPS)]
+    for path in cpp_extension.include_paths():
+        cmd += ["-isystem", path]
+    cmd += ["-isystem", os.path.join(cuda_home, "include")]
+    for path in cpp_extension.library_paths():
+        cmd += ["-L" + path, "-Wl,-rpath," + path]
+    cmd += ["-L" + str(PACKAGE), "-Wl,-rpath,$ORIGIN", "-lanemoi_sm100", "-lc10", "-lc10_cuda", "-ltorch_cpu",
+            "-ltorch_cuda", "-ltorch"]
+    done = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if done.returncode != 0:
+        raise RuntimeError(f"g++ failed on torch_ops.cpp:\n{done.stdout}")
+    return TORCH_OPS
+
+
 if __name__ == "__main__":
     print(build(force=True, verbose=True))
+    print(build_torch_ops(force=True))
