@@ -42,21 +42,28 @@ __host__ __device__ inline int64_t scratch_ints(int H, int R) {
   return (int64_t)H * (kBins + 8 + kStat * (int64_t)R);
 }
 
+// A CTA counts the keys of one half of the key range (blockIdx.z) in its chunk of a head: 64 KB of
+// shared-memory bins, so that it fits on an SM beside one CTA of the prefix rows' attention launch,
+// which runs on a side stream at the same time (with all 128 KB of bins in one CTA the histogram
+// waited for those long CTAs to retire).  The map is L2-resident; reading it twice costs little.
+constexpr int kHalfBins = kBins / 2;
 __global__ void __launch_bounds__(kHistThreads) hist_kernel(const unsigned short* prob,
                                                             int64_t items, int chunks,
                                                             int* hist) {
   extern __shared__ int local[];
-  for (int i = threadIdx.x; i < kBins; i += kHistThreads) local[i] = 0;
+  for (int i = threadIdx.x; i < kHalfBins; i += kHistThreads) local[i] = 0;
   __syncthreads();
-  const int head = blockIdx.y;
+  const int head = blockIdx.y, half = blockIdx.z;
   const int64_t per = (items + chunks - 1) / chunks;
   const int64_t lo = (int64_t)blockIdx.x * per, hi = min(items, lo + per);
   const unsigned short* src = prob + (int64_t)head * items;
-  for (int64_t i = lo + threadIdx.x; i < hi; i += kHistThreads)
-    atomicAdd(&local[__ldg(src + i) & 0x7fff], 1);
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kHistThreads) {
+    const int key = __ldg(src + i) & 0x7fff;
+    if ((key >> 14) == half) atomicAdd(&local[key & (kHalfBins - 1)], 1);
+  }
   __syncthreads();
-  int* out = hist + (int64_t)head * kBins;
-  for (int i = threadIdx.x; i < kBins; i += kHistThreads)
+  int* out = hist + (int64_t)head * kBins + half * kHalfBins;
+  for (int i = threadIdx.x; i < kHalfBins; i += kHistThreads)
     if (local[i]) atomicAdd(out + i, local[i]);
 }
 
@@ -617,7 +624,7 @@ extern "C" int anemoi_sm100_route_anchored(const anemoi_sm100_shape* shape, cons
   int* thr = hist_anchor + (int64_t)H * kBins;
   int* stat = thr + (int64_t)H * 16;
   if (cudaMemsetAsync(hist, 0, (size_t)H * kBins * 8, st) != cudaSuccess) return ANEMOI_SM100_ELAUNCH;
-  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBins * 4) !=
+  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kHalfBins * 4) !=
       cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
   const unsigned short* prob = static_cast<const unsigned short*>(probability);
@@ -625,7 +632,7 @@ extern "C" int anemoi_sm100_route_anchored(const anemoi_sm100_shape* shape, cons
   const int factor = shape->query_block / 64, prefix_stages = rec::prefix_stages(*shape);
   const int lowest_code = n4 ? 1 : (n8 ? 2 : 3);
   const dim3 rows((R + kRowWarps - 1) / kRowWarps, H);
-  hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, hist);
+  hist_kernel<<<dim3(chunks, H, 2), kHistThreads, kHalfBins * 4, st>>>(prob, items, chunks, hist);
   anchor_hist_kernel<<<dim3((anchor_count + 255) / 256, H), 256, 0, st>>>(prob, items, anchor_ids,
                                                                            anchor_count, hist_anchor);
   threshold_kernel<<<H, 1024, 0, st>>>(hist, nullptr, thr, 16, 0, n16, n16 + n8, retained);
@@ -701,15 +708,14 @@ extern "C" int anemoi_sm100_route(const anemoi_sm100_shape* shape, const void* p
   // Function attributes belong to a device: the opt-in is made at every call (a cheap host-side
   // driver call), so a process that routes on several GPUs, or from several host threads,
   // never launches the kernel without the opt-in for its dynamic shared memory.
-  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBins * 4) !=
+  if (cudaFuncSetAttribute(hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kHalfBins * 4) !=
       cudaSuccess)
     return ANEMOI_SM100_ELAUNCH;
-  // about two waves of histogram CTAs (one per SM: the bins fill its shared memory), each
-  // with at least 8192 items
+  // about two waves of histogram CTAs per key-range half, each with at least 8192 items
   const int chunks = (int)max((int64_t)1, min(min((int64_t)16, items / 8192), (int64_t)((296 + H / 2) / H)));
   const int factor = shape->query_block / 64, prefix_stages = rec::prefix_stages(*shape);
   const dim3 rows((R + kRowWarps - 1) / kRowWarps, H);
-  hist_kernel<<<dim3(chunks, H), kHistThreads, kBins * 4, st>>>(prob, items, chunks, sc.hist);
+  hist_kernel<<<dim3(chunks, H, 2), kHistThreads, kHalfBins * 4, st>>>(prob, items, chunks, sc.hist);
   threshold_kernel<<<H, 1024, 0, st>>>(sc.hist, nullptr, sc.thr, 8, 0, n16, n16 + n8, n16 + n8 + n4);
   rowstat_kernel<<<rows, kRowWarps * 32, 0, st>>>(prob, R, sc.thr, sc.stat);
   headscan_kernel<<<H, 1024, 0, st>>>(R, sc.thr, sc.stat, factor, prefix_stages, prefix_phase,
