@@ -539,12 +539,18 @@ def run_ours(args) -> None:
     # ---- timed: end to end from pinned host memory ----
     hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
     hout = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
-    if world == 1:
+    host_call = None
+    if world == 1 or exchange is not None:
         # the library's host-input entry: head groups on three streams, so that the copy of one
-        # group runs under the layer of another (heads are independent; same result bit for bit)
+        # group runs under the layer of another (heads are independent; same result bit for bit).
+        # With N > 1 every rank holds its rows on its host and each head group goes through the
+        # peer-store exchange.
         from anemoi_b200 import HostAttention
 
-        host_call = HostAttention(device, group_heads=args.e2e_group_heads)
+        # sharded: at least two heads per rank and group (a group's prefix rows are one long CTA per tile)
+        group_heads = (args.e2e_group_heads if world == 1
+                       else max(-(-args.e2e_group_heads // world) * world, 2 * world))
+        host_call = HostAttention(device, group_heads=group_heads, sharded=world > 1)
 
         def e2e_step():
             host_call(hq, hk, hv, hout, layout=layout, layer=0, sparse_config=sparse,
@@ -567,7 +573,9 @@ def run_ours(args) -> None:
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item())
-    e2e_matches = bool(torch.equal(hout.to(device), out)) if world == 1 else None
+    e2e_matches = bool(torch.equal(hout.to(device), out)) if host_call is not None else None
+    if host_call is not None:
+        host_call.close()
 
     # ---- N > 1: the sharded result against an unsharded run of one head (outside the timing) ----
     sharded_ok = None
@@ -623,6 +631,8 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": int(out.numel() * out.element_size()),
                     "path": (f"HostAttention: head groups of {args.e2e_group_heads} on three streams, one strided "
                              "copy per group and tensor" if world == 1 else
+                             "HostAttention, sharded: per rank and head group, copy in its rows, peer-store exchange, "
+                             "layer, exchange back, copy out, on three streams" if host_call is not None else
                              "per rank: copy in its sequence shard, Ulysses layer, copy out"),
                     "equals_device_resident_result": e2e_matches},
             # kernels of this library launched per step, counted by the ctypes layer as it calls them

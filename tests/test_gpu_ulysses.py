@@ -58,6 +58,21 @@ def _worker(rank, world, port, results):
             got = ulysses.ulysses_attention(*mine, local, exchange=peer, producer=(wq, wk, cos, sin, 1e-6))
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(got, want))
+            # the host-input entry in its sharded mode: this rank's rows from pinned host memory,
+            # head groups of two (one head per rank and group), two passes (buffer reuse)
+            from anemoi_b200 import HostAttention
+
+            hq, hk, hv = (t.cpu().contiguous().pin_memory() for t in mine)
+            hout = torch.empty_like(hq).pin_memory()
+            runner = HostAttention(torch.device("cuda", rank), group_heads=world, sharded=True)
+            try:
+                for _ in range(2):
+                    hout.fill_(float("nan"))
+                    runner(hq, hk, hv, hout, **kw)
+                    torch.cuda.synchronize()
+                    ok = ok and bool(torch.equal(hout, full[:, lo : lo + rows[rank]].cpu()))
+            finally:
+                runner.close()
         finally:
             peer.close()
         results[rank] = ok
