@@ -64,15 +64,18 @@ def _worker(rank, world, port, results):
 
             hq, hk, hv = (t.cpu().contiguous().pin_memory() for t in mine)
             hout = torch.empty_like(hq).pin_memory()
-            runner = HostAttention(torch.device("cuda", rank), group_heads=world, sharded=True)
-            try:
-                for _ in range(2):
-                    hout.fill_(float("nan"))
-                    runner(hq, hk, hv, hout, **kw)
-                    torch.cuda.synchronize()
-                    ok = ok and bool(torch.equal(hout, full[:, lo : lo + rows[rank]].cpu()))
-            finally:
-                runner.close()
+            # groups of `world` heads, and groups of 3 * world with a shorter last group (two
+            # exchanges of different sizes alive at once)
+            for group_heads in (world, 3 * world):
+                runner = HostAttention(torch.device("cuda", rank), group_heads=group_heads, sharded=True)
+                try:
+                    for _ in range(2):
+                        hout.fill_(float("nan"))
+                        runner(hq, hk, hv, hout, **kw)
+                        torch.cuda.synchronize()
+                        ok = ok and bool(torch.equal(hout, full[:, lo : lo + rows[rank]].cpu()))
+                finally:
+                    runner.close()
         finally:
             peer.close()
         results[rank] = ok
