@@ -1,20 +1,24 @@
 """Ulysses sequence<->head exchange around ``anemoi_attention`` for 1/2/4/8 B200s of one node.
 
-Every rank holds a contiguous slice of the packed sequence with all heads.  One
-all-to-all carries q, k and v together to head-sharded form (each rank: the whole
-sequence, ``heads / world`` heads), attention runs on the local heads, and a second
-all-to-all brings the output back to sequence-sharded form.  Heads are independent
-in every stage of the attention path, so the sharded result is bit-identical to the
+Every rank holds a contiguous slice of the packed sequence with all heads.  q, k and v travel
+together to head-sharded form (each rank: the whole sequence, ``heads / world`` heads), attention
+runs on the local heads, and the output travels back to sequence-sharded form.  Heads are
+independent in every stage of the attention path, so the sharded result is bit-identical to the
 single-GPU result.
 
-Follows the reference's custom Ulysses path
+Two transports.  ``PeerExchange``: the relayout kernels store straight into the other ranks'
+memory over NVLink (regions mapped with CUDA IPC) and hand over with one flag word per source
+rank; no collective call, send buffer, pack or merge pass is on the per-layer path, and the
+qk-norm + rotary step in front of the exchange can ride on the stores.  ``all_to_all_single``
+(NCCL): pack kernel, collective, attention on strided views of the receive buffer, collective,
+merge kernel, optionally pipelined by head groups.
+
+Both follow the reference's custom Ulysses path
 (anemoi/models/minimax_h3/solengine/models/minimax_h3/optimized/ulysses_custom.py:36-165,
-relayout.py:83-162): packed destination-major send buffer, explicit split sizes for
-uneven shards (``tensor_split`` row counts, gathered once per group and cached),
-plain ``all_to_all_single`` without the functional-collective wrapper.  The relayouts
-are CUDA copy kernels of this library instead of Triton kernels, and the head-sharded
-receive buffer is consumed in place by the preparation kernel (strided Q/K/V views),
-so no unpack pass exists.
+relayout.py:83-162): packed destination-major layout, explicit row counts for uneven shards
+(``tensor_split``, gathered once per group and cached).  The relayouts are CUDA kernels of this
+library instead of Triton kernels, and the head-sharded receive buffer is consumed in place by
+the preparation kernel (strided Q/K/V views), so no unpack pass exists.
 """
 
 from __future__ import annotations
