@@ -346,8 +346,12 @@ def run_reference(args) -> None:
         return
     times = []
     last = None
-    for i in range(args.warmup + args.steps):
-        last = cpu_sample(WORKLOAD, query_blocks=args.cpu_query_blocks, seed=1 + i)
+    # every step is a bounded sample (one head, some query blocks); with many steps the samples get
+    # fewer query blocks each, so that the whole run stays within a few minutes
+    total_steps = args.warmup + args.steps
+    blocks = args.cpu_query_blocks if total_steps <= 5 else max(8, min(args.cpu_query_blocks, 160 // total_steps))
+    for i in range(total_steps):
+        last = cpu_sample(WORKLOAD, query_blocks=blocks, seed=1 + i)
         if i >= args.warmup:
             times.append(last["layer_seconds"])
     mean_s = sum(times) / len(times)
