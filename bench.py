@@ -651,6 +651,33 @@ def run_ours(args) -> None:
                          "peak_source": f"{peak_kind} bf16 GEMM {bf16} TFLOP/s x (1, 2, 4) for fp16, 8-bit, NVFP4 "
                                         "cells, weighted by executed FLOPs"},
         }
+        # The HBM-side stages against the measured copy bandwidth (and the nominal 8 TB/s): algorithmic
+        # bytes / CUDA-event time.  Preparation: Q, K, V read once, V once more for its per-channel
+        # amax, every operand record written once.  Routing (draft + route): the pools read, the fp16
+        # map written once and read three times (histogram, row counts, lists), the lists written.
+        # Draft and route run beside the prefix rows' launch of the side stream, so their event
+        # times include the SMs they share with it.
+        hbm = float(peaks["hbm_gbs"])
+        d_, r_ = w["dim"], blocks
+        stages_all = math.ceil(w["prefix"] / 64) + r_ * (qb // 64)
+        rec_bytes = heads_local * (r_ * qb * d_ * 2 + stages_all * 2 * 64 * d_ * 2                       # fp16
+                                   + (r_ + math.ceil(w["prefix"] / qb)) * qb * d_ + stages_all * 2 * 64 * d_  # int8
+                                   + r_ * (qb * d_ // 2 + (d_ // 64) * 512) + stages_all * (64 * d_ + (d_ // 64) * 512 + 512)
+                                   + 2 * r_ * d_ * 2)
+        in_bytes = heads_local * s_total * d_ * 2 * 4
+        route_bytes = heads_local * (4 * r_ * r_ * 2 + 2 * r_ * d_ * 2) + heads_local * 4 * (
+            (n16 + n8 + n4) * (qb // 64) + r_ * p)
+        prep_ms, rt_ms = stages.get("prepare"), (stages.get("draft", 0.0) + stages.get("route", 0.0))
+        if prep_ms and rt_ms:
+            line["hbm_stages"] = {
+                "prepare": {"bytes": in_bytes + rec_bytes, "GBs": (in_bytes + rec_bytes) / (prep_ms * 1e-3) / 1e9,
+                            "frac_of_measured": (in_bytes + rec_bytes) / (prep_ms * 1e-3) / 1e9 / hbm,
+                            "frac_of_nominal_8TBs": (in_bytes + rec_bytes) / (prep_ms * 1e-3) / 1e9 / 8000.0},
+                "draft_route": {"bytes": route_bytes, "GBs": route_bytes / (rt_ms * 1e-3) / 1e9,
+                                "frac_of_measured": route_bytes / (rt_ms * 1e-3) / 1e9 / hbm,
+                                "frac_of_nominal_8TBs": route_bytes / (rt_ms * 1e-3) / 1e9 / 8000.0,
+                                "note": "the 50.6 MB map stays in L2; the stage is launch- and latency-bound"},
+                "peak_source": f"{peak_kind} copy bandwidth {hbm} GB/s"}
         if world == 1:
             from anemoi_b200 import native
 
